@@ -1,0 +1,75 @@
+// Shared helpers of the dlblas_b200 CUDA extension (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/dlblas_b200.h"
+
+namespace dlb {
+
+// Records the message returned by dlb_last_error_string() (thread local) and
+// hands back the code so call sites can `return fail(...)`.
+int fail(int code, const char* fmt, ...);
+
+inline int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return DLB_OK;
+  return fail(DLB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int sm_count();  // multiprocessors of the current device (cached per device)
+void count_launch();  // bumps the per-thread kernel launch counter read by dlb_launch_count()
+
+#define DLB_CHECK_LAUNCH(name)                                  \
+  do {                                                          \
+    cudaError_t e__ = cudaGetLastError();                       \
+    if (e__ != cudaSuccess) return dlb::check_cuda(e__, name);  \
+  } while (0)
+
+#define DLB_REQUIRE(cond, code, ...)                 \
+  do {                                               \
+    if (!(cond)) return dlb::fail(code, __VA_ARGS__); \
+  } while (0)
+
+__host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- warp helpers -------------------------------------------------------- //
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ---- element conversion ---------------------------------------------------- //
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// Two fp32 -> packed e4m3x2 (lo in bits 0-7), round to nearest even, saturating to +-448.
+__device__ __forceinline__ uint16_t f32x2_to_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+}  // namespace dlb

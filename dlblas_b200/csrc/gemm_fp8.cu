@@ -1,0 +1,724 @@
+// Block-scaled FP8 (e4m3) GEMMs for sm_100a: dense and grouped over ragged expert
+// segments.  One persistent, warp-specialised kernel:
+//
+//   warp 8  (1 thread)  TMA producer: A tile [128 x 128B] and B tile [BN x 128B] per
+//                       128-wide K block into a ring of 128B-swizzled smem stages.
+//   warp 9  (1 thread)  issues tcgen05.mma kind::f8f6f4 (128 x BN x 32, four per K block)
+//                       into a ring of TMEM accumulators, one accumulator per K block.
+//   warps 0-7           promotion + epilogue: tcgen05.ld each K block's partial product,
+//                       acc += partial * a_scale[row, kb] * b_scale[nblk, kb] on the CUDA
+//                       cores (the scales are arbitrary fp32, so the hardware block-scale
+//                       path, which wants UE8M0 scales, does not apply), then the epilogue.
+//
+// The arithmetic follows dlblas/kernels/fp8_gemm.py:50-59 and
+// dlblas/layers/moe/kernels/blocked_fp8_fused_moe.py:95-156 of the reference: fp32
+// accumulation over K blocks in increasing order, one rounding to the output type.
+//
+// All mbarrier waits are bounded: a wait that exceeds its time limit raises a CTA-wide
+// abort flag, every role leaves its loop, the status word is set to DLB_STATUS_TIMEOUT
+// and the kernel returns after draining what it issued.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace dlb {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 128;              // bytes == elements (e4m3)
+constexpr int A_STAGE_BYTES = BM * BK;
+constexpr int EPI_WARPS = 8;         // two warpgroups
+constexpr int PRODUCER_WARP = 8;
+constexpr int MMA_WARP = 9;
+constexpr int NUM_THREADS = 320;
+constexpr int TMEM_COLS = 512;
+
+struct GemmArgs {
+  const float* a_s;
+  long long a_s_rs, a_s_ks;   // a_s[row * rs + kb * ks]
+  const float* b_s;
+  long long b_s_es;           // per-expert stride; inside: [nblk * kblocks + kb]
+  void* c;
+  long long ldc;
+  float* q_scale;             // SWIGLU_QUANT: [rows, n_half/128]
+  const int4* tiles;          // nullptr: dense, M tiles derived from m
+  int m, n, k;
+  int n_half;                 // SWIGLU_QUANT: intermediate size (n / 2)
+  int num_m_tiles_static;
+  int num_n_tiles;
+  const long long* sorted_idx;
+  const float* weights;
+  int* status;
+  unsigned long long timeout_ns;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the CTA is aborting (set by this or another thread).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 0xffu) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 lanes x 16 consecutive columns, one fp32 per register.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+// Waits for this thread's outstanding tcgen05.ld.  The staging registers are listed as
+// read-write operands so the compiler cannot schedule arithmetic on them above the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+               :
+               : "memory");
+}
+
+// K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);  // start address
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                        // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+
+// kind::f8f6f4, A and B e4m3 K-major, fp32 accumulate, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t make_idesc(int bn) {
+  return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int BN> struct Cfg {
+  static constexpr int B_STAGE_BYTES = BN * BK;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TMEM_BUFS = TMEM_COLS / BN;
+  static constexpr int SEG = BN / 4;  // columns per thread segment (two segments per thread)
+  // dynamic smem: stages | barriers (full, empty, tmem_full, tmem_empty) | misc
+  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 2 * TMEM_BUFS + 2;
+  static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
+  static constexpr int XCHG_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // 2 tiles x 2 warpgroups x 128 floats
+  static constexpr int SMEM_BYTES = XCHG_OFF + 4 * BM * 4 + 1024;  // + slack for 1024 B alignment
+};
+
+struct Tile {
+  int e, row0, rows, n0;
+};
+
+template <int BN, int MODE>
+__device__ __forceinline__ Tile decode_tile(const GemmArgs& g, int t) {
+  Tile ti;
+  const int m_tile = t / g.num_n_tiles;
+  const int n_tile = t - m_tile * g.num_n_tiles;
+  if (g.tiles != nullptr) {
+    const int4 v = __ldg(g.tiles + 1 + m_tile);
+    ti.e = v.x;
+    ti.row0 = v.y;
+    ti.rows = v.z;
+  } else {
+    ti.e = 0;
+    ti.row0 = m_tile * BM;
+    ti.rows = min(BM, g.m - ti.row0);
+  }
+  ti.n0 = n_tile * (MODE == DLB_EPI_SWIGLU_QUANT ? BN / 2 : BN);
+  return ti;
+}
+
+template <typename OutT> struct Pack;
+template <> struct Pack<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t two(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+template <> struct Pack<__half> {
+  static __device__ __forceinline__ uint32_t two(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
+// Stores NCOLS accumulators (a compile-time count, multiple of 8) of one row; only the first
+// `valid` columns exist.  dst is 16-byte aligned.  Fully unrolled so `acc` stays in registers.
+template <typename OutT, int NCOLS>
+__device__ __forceinline__ void store_row(OutT* dst, const float (&acc)[NCOLS], int valid) {
+  if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+    for (int j = 0; j < NCOLS; j += 4) {
+      if (j < valid)
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + j) =
+            make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < NCOLS; j += 8) {
+      if (j < valid) {
+        uint4 v;
+        v.x = Pack<OutT>::two(acc[j], acc[j + 1]);
+        v.y = Pack<OutT>::two(acc[j + 2], acc[j + 3]);
+        v.z = Pack<OutT>::two(acc[j + 4], acc[j + 5]);
+        v.w = Pack<OutT>::two(acc[j + 6], acc[j + 7]);
+        *reinterpret_cast<uint4*>(dst + j) = v;
+      }
+    }
+  }
+}
+
+template <int BN, int MODE, typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const GemmArgs g) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + C::BAR_OFF;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + C::TMEM_BUFS + b); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * C::STAGES + 2 * C::TMEM_BUFS);
+  const uint32_t xchg_bar = drain_bar + 8u;
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + C::MISC_OFF);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::MISC_OFF + 4);
+  float* xchg = reinterpret_cast<float*>(smem + C::XCHG_OFF);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kblocks = g.k / BK;
+  const int num_m_tiles = g.tiles != nullptr ? __ldg(reinterpret_cast<const int*>(g.tiles)) : g.num_m_tiles_static;
+  const int total_tiles = num_m_tiles * g.num_n_tiles;
+  const unsigned long long limit = g.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < C::TMEM_BUFS; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), EPI_WARPS);
+    }
+    mbar_init(drain_bar, 1);
+    mbar_init(xchg_bar, EPI_WARPS * 32);
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;   // private flag of the drain waits
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(const_cast<uint32_t*>(tmem_holder))),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == PRODUCER_WARP) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const Tile ti = decode_tile<BN, MODE>(g, t);
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, limit)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+          mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, kb * BK, ti.row0, full_bar(s));
+          if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
+            // gate rows [n0, n0+128) and up rows [n_half + n0, ...+128) of expert e
+            tma_load_2d(b_dst, &tmap_b, kb * BK, ti.e * g.n + ti.n0, full_bar(s));
+            tma_load_2d(b_dst + 128 * BK, &tmap_b, kb * BK, ti.e * g.n + g.n_half + ti.n0, full_bar(s));
+          } else {
+#pragma unroll
+            for (int h = 0; h < BN / 128; ++h)
+              tma_load_2d(b_dst + h * 128 * BK, &tmap_b, kb * BK, ti.e * g.n + ti.n0 + h * 128, full_bar(s));
+          }
+        }
+      }
+      if (!ok) {
+        // drain: give the loads of the last STAGES iterations a bounded chance to land
+        const uint32_t first = it > (uint32_t)C::STAGES ? it - C::STAGES : 0u;
+        for (uint32_t i = first; i < it; ++i)
+          mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1u, abort_flag + 1, 20000000ull);
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const int b = it % C::TMEM_BUFS;
+          if (!mbar_wait(full_bar(s), (it / C::STAGES) & 1u, abort_flag, limit) ||
+              !mbar_wait(tempty_bar(b), ((it / C::TMEM_BUFS) & 1u) ^ 1u, abort_flag, limit)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + s * C::STAGE_BYTES;
+          const uint64_t a_desc = make_smem_desc(a_addr);
+          const uint64_t b_desc = make_smem_desc(a_addr + A_STAGE_BYTES);
+          const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
+#pragma unroll
+          for (int kk = 0; kk < BK / 32; ++kk) {
+            // +32 bytes along K inside the 128 B swizzle row == +2 in the (addr >> 4) field
+            tc_mma_f8(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(empty_bar(s));   // smem stage reusable once these MMAs retire
+          tc_commit(tfull_bar(b));   // accumulator ready for the promotion warps
+        }
+      }
+      if (!ok) {
+        tc_commit(drain_bar);
+        mbar_wait(drain_bar, 0, abort_flag + 1, 20000000ull);
+      }
+    }
+  } else {
+    // ---- promotion + epilogue warps ------------------------------------------
+    const int wg = warp >> 2;                 // 0 or 1
+    const int quad = warp & 3;                // TMEM lane quadrant of this warp
+    const int r = quad * 32 + lane;           // row inside the tile
+    constexpr int SEG = C::SEG;
+    // TMEM column offsets of this thread's two segments, and matching output columns
+    int seg_col[2];
+    if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
+      seg_col[0] = wg * SEG;                  // gate columns
+      seg_col[1] = BN / 2 + wg * SEG;         // up columns
+    } else {
+      seg_col[0] = wg * 2 * SEG;
+      seg_col[1] = wg * 2 * SEG + SEG;
+    }
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    uint32_t it = 0;
+    uint32_t tile_no = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
+      const Tile ti = decode_tile<BN, MODE>(g, t);
+      const bool row_ok = r < ti.rows;
+      const long long p = (long long)ti.row0 + r;          // row of A / sorted position
+      const float* as_ptr = g.a_s + (row_ok ? p : (long long)ti.row0) * g.a_s_rs;
+      // scale blocks of the two segments
+      const float* bs_ptr[2];
+      {
+        const float* be = g.b_s + (long long)ti.e * g.b_s_es;
+        int nb0, nb1;
+        if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
+          nb0 = ti.n0 / 128;
+          nb1 = (g.n_half + ti.n0) / 128;
+        } else {
+          nb0 = (ti.n0 + seg_col[0]) / 128;
+          nb1 = (ti.n0 + seg_col[1]) / 128;
+          const int nb_max = (g.n + 127) / 128 - 1;
+          nb0 = min(nb0, nb_max);
+          nb1 = min(nb1, nb_max);
+        }
+        bs_ptr[0] = be + (long long)nb0 * kblocks;
+        bs_ptr[1] = be + (long long)nb1 * kblocks;
+      }
+      float acc[2 * SEG];
+#pragma unroll
+      for (int j = 0; j < 2 * SEG; ++j) acc[j] = 0.f;
+
+      float a_sc = __ldg(as_ptr);
+      float b_sc0 = __ldg(bs_ptr[0]);
+      float b_sc1 = __ldg(bs_ptr[1]);
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int b = it % C::TMEM_BUFS;
+        // prefetch the next block's scales while waiting for the accumulator
+        float a_nx = 0.f, b_nx0 = 0.f, b_nx1 = 0.f;
+        if (kb + 1 < kblocks) {
+          a_nx = __ldg(as_ptr + (long long)(kb + 1) * g.a_s_ks);
+          b_nx0 = __ldg(bs_ptr[0] + kb + 1);
+          b_nx1 = __ldg(bs_ptr[1] + kb + 1);
+        }
+        if (!mbar_wait(tfull_bar(b), (it / C::TMEM_BUFS) & 1u, abort_flag, limit)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float sc0 = a_sc * b_sc0;
+        const float sc1 = a_sc * b_sc1;
+        const uint32_t buf_addr = lane_addr + (uint32_t)(b * BN);
+        // 16-column chunks, two staging buffers: the load of chunk c+1 is in flight
+        // while chunk c is folded into the accumulators.
+        constexpr int CH = 2 * SEG / 16;
+        uint32_t v0[16], v1[16];
+        tmem_ld16(buf_addr + seg_col[0], v0);
+#pragma unroll
+        for (int c = 0; c < CH; c += 2) {
+          {
+            const int cc = c + 1;
+            const int col = (cc * 16 < SEG) ? seg_col[0] + cc * 16 : seg_col[1] + cc * 16 - SEG;
+            tmem_ld_wait(v0);
+            tmem_ld16(buf_addr + col, v1);
+            const float sc = (c * 16 < SEG) ? sc0 : sc1;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(__uint_as_float(v0[j]), sc, acc[c * 16 + j]);
+          }
+          {
+            const int cc = c + 2;
+            tmem_ld_wait(v1);
+            if (cc < CH) {
+              const int col = (cc * 16 < SEG) ? seg_col[0] + cc * 16 : seg_col[1] + cc * 16 - SEG;
+              tmem_ld16(buf_addr + col, v0);
+            } else {
+              // all columns of this accumulator are in registers: hand it back to the MMA warp
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_bar(b));
+            }
+            const float sc = ((c + 1) * 16 < SEG) ? sc0 : sc1;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              acc[(c + 1) * 16 + j] = fmaf(__uint_as_float(v1[j]), sc, acc[(c + 1) * 16 + j]);
+          }
+        }
+        a_sc = a_nx;
+        b_sc0 = b_nx0;
+        b_sc1 = b_nx1;
+      }
+      if (!ok) break;
+
+      // ---- epilogue ---------------------------------------------------------
+      if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
+        // reference rounding points: GEMM1 output -> OutT, silu(gate)*up -> OutT, then
+        // scale = absmax * (1/448), q = h / scale (dlblas/kernels/moe.py:398-417).
+        float h[SEG];
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < SEG; ++j) {
+          const float gt = to_f32<OutT>(from_f32<OutT>(acc[j]));
+          const float up = to_f32<OutT>(from_f32<OutT>(acc[SEG + j]));
+          const float sv = gt / (1.f + __expf(-gt));
+          h[j] = to_f32<OutT>(from_f32<OutT>(sv * up));
+          amax = fmaxf(amax, fabsf(h[j]));
+        }
+        // the two warpgroups hold the two halves of each row's 128-wide quantisation group:
+        // exchange the partial maxima through smem (double-buffered by tile parity, one
+        // bounded barrier phase per tile)
+        float* xb = xchg + (tile_no & 1u) * 2 * BM;
+        xb[wg * BM + r] = amax;
+        mbar_arrive(xchg_bar);
+        if (!mbar_wait(xchg_bar, tile_no & 1u, abort_flag, limit)) {
+          ok = false;
+          break;
+        }
+        amax = fmaxf(amax, xb[(wg ^ 1) * BM + r]);
+        const float scale = amax * (1.0f / 448.0f);
+        if (row_ok) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(g.c) + p * g.ldc + ti.n0 + wg * SEG;
+#pragma unroll
+          for (int j = 0; j < SEG; j += 16) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint16_t lo = f32x2_to_e4m3x2(h[j + 4 * q] / scale, h[j + 4 * q + 1] / scale);
+              const uint16_t hi = f32x2_to_e4m3x2(h[j + 4 * q + 2] / scale, h[j + 4 * q + 3] / scale);
+              w[q] = (uint32_t)lo | ((uint32_t)hi << 16);
+            }
+            *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          if (wg == 0) g.q_scale[p * (long long)(g.n_half / 128) + ti.n0 / 128] = scale;
+        }
+      } else {
+        if (row_ok) {
+          long long crow = p;
+          if constexpr (MODE == DLB_EPI_SCATTER_WEIGHT) {
+            crow = g.sorted_idx[p];
+            const float w = g.weights[crow];
+#pragma unroll
+            for (int j = 0; j < 2 * SEG; ++j) acc[j] *= w;
+          }
+          const int col0 = ti.n0 + seg_col[0];
+          OutT* dst = reinterpret_cast<OutT*>(g.c) + crow * g.ldc + col0;
+          const int ncols = min(2 * SEG, g.n - col0);   // n % 8 == 0
+          store_row<OutT, 2 * SEG>(dst, acc, ncols);
+        }
+      }
+    }
+  }
+
+  // ---- teardown ----------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0 && g.status != nullptr) atomicExch(g.status, DLB_STATUS_TIMEOUT);
+  if (warp == MMA_WARP) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side -----------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D map over a row-major [rows, k] e4m3 matrix, box = 128 rows x 128 bytes, 128 B swizzle.
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return fail(DLB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t gdim[2] = {k, rows};
+  const cuuint64_t gstride[1] = {k};
+  const cuuint32_t box[2] = {BK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(DLB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return DLB_OK;
+}
+
+template <int BN, int MODE, typename OutT>
+int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int grid, cudaStream_t st) {
+  auto kern = gemm_fp8_kernel<BN, MODE, OutT>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES),
+                        "cudaFuncSetAttribute(gemm_fp8_kernel)");
+    if (rc != DLB_OK) return rc;
+    configured[dev] = true;
+  }
+  kern<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(ma, mb, g);
+  count_launch();
+  DLB_CHECK_LAUNCH("gemm_fp8_kernel");
+  return DLB_OK;
+}
+
+template <int MODE>
+int launch_typed(int bn, int c_dtype, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int grid,
+                 cudaStream_t st) {
+  if (bn == 256) {
+    if (c_dtype == DLB_BF16) return launch_one<256, MODE, __nv_bfloat16>(ma, mb, g, grid, st);
+    if (c_dtype == DLB_F16) return launch_one<256, MODE, __half>(ma, mb, g, grid, st);
+    if constexpr (MODE != DLB_EPI_SWIGLU_QUANT)
+      if (c_dtype == DLB_F32) return launch_one<256, MODE, float>(ma, mb, g, grid, st);
+  } else {
+    if constexpr (MODE != DLB_EPI_SWIGLU_QUANT) {
+      if (c_dtype == DLB_BF16) return launch_one<128, MODE, __nv_bfloat16>(ma, mb, g, grid, st);
+      if (c_dtype == DLB_F16) return launch_one<128, MODE, __half>(ma, mb, g, grid, st);
+      if (c_dtype == DLB_F32) return launch_one<128, MODE, float>(ma, mb, g, grid, st);
+    }
+  }
+  return fail(DLB_ERR_INVALID, "unsupported output dtype %d for this GEMM epilogue", c_dtype);
+}
+
+int check_device() {
+  static int ok[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && ok[dev] == 1) return DLB_OK;
+  cudaDeviceProp prop;
+  int rc = check_cuda(cudaGetDeviceProperties(&prop, dev), "cudaGetDeviceProperties");
+  if (rc != DLB_OK) return rc;
+  if (prop.major != 10) return fail(DLB_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only",
+                                    dev, prop.major, prop.minor);
+  if (dev < 64) ok[dev] = 1;
+  return DLB_OK;
+}
+
+constexpr unsigned long long DEFAULT_TIMEOUT_NS = 2000000000ull;  // 2 s per barrier wait
+
+}  // namespace
+}  // namespace dlb
+
+using namespace dlb;
+
+extern "C" int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int64_t a_s_row_stride,
+                            int64_t a_s_kb_stride, const float* b_s, void* c, int c_dtype, int64_t m, int64_t n,
+                            int64_t k, int32_t* status, void* stream) {
+  DLB_REQUIRE(m >= 0 && n > 0 && k > 0, DLB_ERR_INVALID, "fp8_gemm: bad sizes m=%lld n=%lld k=%lld", (long long)m,
+              (long long)n, (long long)k);
+  DLB_REQUIRE(k % 128 == 0, DLB_ERR_INVALID, "fp8_gemm: k=%lld must be a multiple of 128", (long long)k);
+  DLB_REQUIRE(n % 8 == 0, DLB_ERR_INVALID, "fp8_gemm: n=%lld must be a multiple of 8", (long long)n);
+  DLB_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), DLB_ERR_INVALID, "fp8_gemm: size too large");
+  if (m == 0) return DLB_OK;
+  DLB_REQUIRE(a && b && a_s && b_s && c, DLB_ERR_INVALID, "fp8_gemm: null pointer");
+  DLB_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 16 == 0), DLB_ERR_INVALID,
+              "fp8_gemm: a, b and c must be 16-byte aligned");
+  int rc = check_device();
+  if (rc != DLB_OK) return rc;
+  CUtensorMap ma, mb;
+  if ((rc = make_map(&ma, a, (uint64_t)m, (uint64_t)k)) != DLB_OK) return rc;
+  if ((rc = make_map(&mb, b, (uint64_t)n, (uint64_t)k)) != DLB_OK) return rc;
+  const int sms = sm_count();
+  const int m_tiles = (int)ceil_div(m, BM);
+  // 256-wide tiles feed the tensor cores best; fall back to 128 when that would leave SMs idle
+  int bn = 256;
+  if (m_tiles * ceil_div(n, 256) < sms) bn = 128;
+  GemmArgs g = {};
+  g.a_s = a_s;
+  g.a_s_rs = a_s_row_stride;
+  g.a_s_ks = a_s_kb_stride;
+  g.b_s = b_s;
+  g.b_s_es = 0;
+  g.c = c;
+  g.ldc = n;
+  g.tiles = nullptr;
+  g.m = (int)m;
+  g.n = (int)n;
+  g.k = (int)k;
+  g.num_m_tiles_static = m_tiles;
+  g.num_n_tiles = (int)ceil_div(n, bn);
+  g.status = status;
+  g.timeout_ns = DEFAULT_TIMEOUT_NS;
+  const long long total = (long long)m_tiles * g.num_n_tiles;
+  const int grid = (int)(total < sms ? total : sms);
+  return launch_typed<DLB_EPI_STORE>(bn, c_dtype, ma, mb, g, grid, (cudaStream_t)stream);
+}
+
+extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a, const void* b, const float* b_s,
+                                    int num_local_experts, int64_t n, int64_t k, const int32_t* tiles, int max_tiles,
+                                    int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
+                                    const int64_t* sorted_idx, const float* weights, int32_t* status, void* stream) {
+  DLB_REQUIRE(rows_a >= 0 && n > 0 && k > 0 && num_local_experts > 0 && max_tiles >= 0, DLB_ERR_INVALID,
+              "grouped_gemm: bad sizes rows=%lld n=%lld k=%lld experts=%d", (long long)rows_a, (long long)n,
+              (long long)k, num_local_experts);
+  DLB_REQUIRE(k % 128 == 0, DLB_ERR_INVALID, "grouped_gemm: k=%lld must be a multiple of 128", (long long)k);
+  DLB_REQUIRE(n % 128 == 0, DLB_ERR_INVALID, "grouped_gemm: n=%lld must be a multiple of 128", (long long)n);
+  DLB_REQUIRE(rows_a < (1ll << 31) && (long long)num_local_experts * n < (1ll << 31) && k < (1ll << 31),
+              DLB_ERR_INVALID, "grouped_gemm: size too large");
+  if (rows_a == 0 || max_tiles == 0) return DLB_OK;
+  DLB_REQUIRE(a && a_s && b && b_s && c && tiles, DLB_ERR_INVALID, "grouped_gemm: null pointer");
+  DLB_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 16 == 0) &&
+                  ((uintptr_t)tiles % 16 == 0),
+              DLB_ERR_INVALID, "grouped_gemm: a, b, c and tiles must be 16-byte aligned");
+  int rc = check_device();
+  if (rc != DLB_OK) return rc;
+  CUtensorMap ma, mb;
+  if ((rc = make_map(&ma, a, (uint64_t)rows_a, (uint64_t)k)) != DLB_OK) return rc;
+  if ((rc = make_map(&mb, b, (uint64_t)num_local_experts * (uint64_t)n, (uint64_t)k)) != DLB_OK) return rc;
+  const int sms = sm_count();
+  GemmArgs g = {};
+  g.a_s = a_s;
+  g.a_s_rs = k / 128;
+  g.a_s_ks = 1;
+  g.b_s = b_s;
+  g.b_s_es = (n / 128) * (k / 128);
+  g.c = c;
+  g.ldc = ldc;
+  g.q_scale = q_scale;
+  g.tiles = reinterpret_cast<const int4*>(tiles);
+  g.m = (int)rows_a;
+  g.n = (int)n;
+  g.k = (int)k;
+  g.n_half = (int)(n / 2);
+  g.sorted_idx = reinterpret_cast<const long long*>(sorted_idx);
+  g.weights = weights;
+  g.status = status;
+  g.timeout_ns = DEFAULT_TIMEOUT_NS;
+  int bn = 256;
+  if (epilogue == DLB_EPI_SWIGLU_QUANT) {
+    DLB_REQUIRE(n % 256 == 0, DLB_ERR_INVALID, "grouped_gemm: swiglu epilogue needs n %% 256 == 0 (n=%lld)",
+                (long long)n);
+    DLB_REQUIRE(q_scale != nullptr, DLB_ERR_INVALID, "grouped_gemm: swiglu epilogue needs q_scale");
+    DLB_REQUIRE(ldc % 16 == 0, DLB_ERR_INVALID, "grouped_gemm: ldc must be a multiple of 16 for e4m3 output");
+    g.num_n_tiles = (int)(n / 256);
+  } else {
+    DLB_REQUIRE(epilogue == DLB_EPI_STORE || epilogue == DLB_EPI_SCATTER_WEIGHT, DLB_ERR_INVALID,
+                "grouped_gemm: unknown epilogue %d", epilogue);
+    if (epilogue == DLB_EPI_SCATTER_WEIGHT)
+      DLB_REQUIRE(sorted_idx && weights, DLB_ERR_INVALID, "grouped_gemm: scatter epilogue needs sorted_idx and weights");
+    DLB_REQUIRE(ldc % 8 == 0, DLB_ERR_INVALID, "grouped_gemm: ldc must be a multiple of 8");
+    if ((long long)max_tiles * ceil_div(n, 256) < sms) bn = 128;
+    g.num_n_tiles = (int)ceil_div(n, bn);
+  }
+  const long long total = (long long)max_tiles * g.num_n_tiles;
+  const int grid = (int)(total < sms ? total : sms);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (epilogue == DLB_EPI_STORE) return launch_typed<DLB_EPI_STORE>(bn, c_dtype, ma, mb, g, grid, st);
+  if (epilogue == DLB_EPI_SCATTER_WEIGHT) return launch_typed<DLB_EPI_SCATTER_WEIGHT>(bn, c_dtype, ma, mb, g, grid, st);
+  return launch_typed<DLB_EPI_SWIGLU_QUANT>(bn, c_dtype, ma, mb, g, grid, st);
+}

@@ -1,0 +1,46 @@
+"""`dlblas.topk_gating` forward (dlblas/kernels/topk_gating.py:245-317 of the reference):
+capacity-limited softmax top-k gating, registered with the op registry under 'topk_gating'."""
+import math
+
+import torch
+
+from .. import ops
+from ..symbolic_var import SymVar
+from ..symbolic_var import Tensor as FakeTensor
+from ..utils import register_dlblas_op
+
+
+def _capacity(num_tokens: int, num_experts: int, capacity_factor: float, min_capacity: int) -> int:
+    """ceil(T / E * capacity_factor), at least min_capacity (topk_gating.py:15-24), computed on the
+    host from the shape: no device round trip."""
+    cap = int(math.ceil((num_tokens / num_experts) * capacity_factor))
+    return max(cap, int(min_capacity))
+
+
+def call(logits: torch.Tensor, k: int, capacity_factor: float = 1.0, min_capacity: int = 2,
+         enable_token_rearrange_opt: bool = False):
+    """Returns (l_aux, token_rearranged_ec_idx int32 [k*T], token_exp_weights [k*T],
+    expert_select_token_idx int64 [E*capacity]).  Both settings of the last flag give the same
+    four outputs in the reference (:256-268); forward only."""
+    t, e = logits.shape
+    capacity = _capacity(t, e, capacity_factor * k, min_capacity)
+    return ops.topk_gating(logits.contiguous(), k, capacity)
+
+
+def bench_fn(logits, k, capacity_factor=1.0, min_capacity=2, enable_token_rearrange_opt=False):
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        call(logits, k, capacity_factor, min_capacity, enable_token_rearrange_opt)
+    start.record()
+    for _ in range(10):
+        call(logits, k, capacity_factor, min_capacity, enable_token_rearrange_opt)
+    end.record()
+    end.synchronize()
+    return start.elapsed_time(end) / 10
+
+
+name = "topk_gating"
+for _dtype in [torch.float16, torch.float32]:
+    _logits = FakeTensor((SymVar("seqLen"), SymVar("experts")), dtype=_dtype, device="cuda")
+    register_dlblas_op(name, None, (_logits, torch.SymInt, torch.SymFloat, torch.SymInt, torch.SymBool), call, bench_fn,
+                       call)

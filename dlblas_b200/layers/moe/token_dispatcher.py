@@ -1,0 +1,334 @@
+"""Expert-parallel token exchange over NCCL (NVLink 5 / NVSwitch), standing in for the DeepEP
+`Buffer` wrappers of the reference (dlblas/layers/moe/token_dispatcher.py:245-602).
+
+One process per GPU; rank r owns experts [r * E_local, (r + 1) * E_local).  Each direction is one
+variable-size all-to-all (`all_to_all_single` with split sizes).  The split sizes come from ONE
+all-gather of a small count matrix followed by ONE device->host copy (the reference synchronises at
+the same point: DeepEP hands back `recv_tokens_per_expert` as a Python list).  Rows are packed and
+unpacked by the permutation / gather kernels of the CUDA extension; the planning below is plain
+torch on small integer tensors and runs on any backend, so it is unit-tested with gloo on CPU.
+"""
+from typing import List, Optional, Tuple, Union
+
+import torch
+import torch.distributed as dist
+
+from ... import _C, ops
+from ...utils.utils import DisposibleTensor
+
+
+class CommEvent:
+    """Event handed out by the async API; `current_stream_wait()` as on DeepEP's EventOverlap."""
+
+    def __init__(self, event: Optional[torch.cuda.Event] = None):
+        self.event = event
+
+    def current_stream_wait(self):
+        if self.event is not None:
+            torch.cuda.current_stream().wait_event(self.event)
+
+
+def _record_event() -> CommEvent:
+    if torch.cuda.is_available():
+        ev = torch.cuda.Event()
+        ev.record()
+        return CommEvent(ev)
+    return CommEvent(None)
+
+
+# ----------------------------------------------------------------------------------------------
+# planning (device agnostic)
+# ----------------------------------------------------------------------------------------------
+class NormalPlan:
+    """Exchange plan of the contiguous ("normal") mode: every token goes once to each rank that owns
+    at least one of its routed experts."""
+
+    def __init__(self):
+        self.dst_pos = None          # int32 [T, W]: row in the send buffer or -1
+        self.send_splits = None      # python lists
+        self.recv_splits = None
+        self.recv_tokens_per_expert = None   # python list, aligned
+        self.num_tokens = 0
+        self.num_send = 0
+        self.num_recv = 0
+
+
+def make_normal_plan(topk_ids: torch.Tensor, world_size: int, rank: int, num_local_experts: int,
+                     group, expert_alignment: int = 128) -> NormalPlan:
+    """topk_ids: [T, k] global expert ids (any negative id = unrouted slot)."""
+    t, k = topk_ids.shape
+    dev = topk_ids.device
+    ids = topk_ids.to(torch.int64)
+    valid = ids >= 0
+    owner = torch.where(valid, ids // num_local_experts, torch.full_like(ids, world_size))
+    need = torch.zeros(t, world_size + 1, dtype=torch.int32, device=dev)
+    need.scatter_(1, owner, 1)
+    need = need[:, :world_size]                                   # [T, W] 0/1
+    per_rank = need.sum(dim=0, dtype=torch.int64)                 # rows sent to each rank
+    offs = torch.cumsum(per_rank, 0) - per_rank
+    within = torch.cumsum(need, dim=0, dtype=torch.int64) - need  # rank of the token among the rank's rows
+    dst_pos = torch.where(need > 0, offs[None, :] + within, torch.full_like(within, -1)).to(torch.int32)
+    per_expert = torch.bincount(ids[valid], minlength=world_size * num_local_experts)[:world_size * num_local_experts]
+    mine = torch.cat([per_rank[:, None], per_expert.view(world_size, num_local_experts)], dim=1).contiguous()
+    gathered = torch.empty(world_size, world_size, num_local_experts + 1, dtype=torch.int64, device=dev)
+    if world_size > 1:
+        dist.all_gather_into_tensor(gathered.view(world_size, -1), mine.view(1, -1), group=group)
+    else:
+        gathered[0] = mine
+    host = gathered.cpu()                                         # the one synchronisation of the dispatch
+    plan = NormalPlan()
+    plan.dst_pos = dst_pos.contiguous()
+    plan.send_splits = host[rank, :, 0].tolist()
+    plan.recv_splits = host[:, rank, 0].tolist()
+    per_exp = host[:, rank, 1:].sum(dim=0)
+    al = expert_alignment
+    plan.recv_tokens_per_expert = [int((c + al - 1) // al * al) for c in per_exp.tolist()]
+    plan.num_tokens = t
+    plan.num_send = int(sum(plan.send_splits))
+    plan.num_recv = int(sum(plan.recv_splits))
+    return plan
+
+
+def localize_ids(ids: torch.Tensor, dest_rank: torch.Tensor, num_local_experts: int) -> torch.Tensor:
+    """ids [n, k] global, dest_rank [n]: ids local to the destination rank, -1 where another rank owns it."""
+    lo = (dest_rank * num_local_experts)[:, None]
+    mine = (ids >= lo) & (ids < lo + num_local_experts)
+    return torch.where(mine, ids - lo, torch.full_like(ids, -1))
+
+
+def _a2a(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, group, world_size: int):
+    if world_size == 1:
+        out.copy_(inp)
+    else:
+        dist.all_to_all_single(out, inp, output_split_sizes=out_splits, input_split_sizes=in_splits, group=group)
+
+
+# ----------------------------------------------------------------------------------------------
+# normal (prefill) mode
+# ----------------------------------------------------------------------------------------------
+class TokenDispatcherNormal:
+    """`DeepEPTokenDispatcherNormal` of the reference (token_dispatcher.py:245-452) over NCCL."""
+
+    def __init__(self, group, num_experts: int = None, num_local_experts: int = None, hidden_size: int = None,
+                 params_dtype: torch.dtype = None, expert_alignment: int = 128):
+        self.group = group
+        self.num_experts = num_experts
+        self.num_local_experts = num_local_experts
+        self.hidden_size = hidden_size
+        self.params_dtype = params_dtype
+        self.expert_alignment = expert_alignment
+        self.world_size = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if (dist.is_available() and dist.is_initialized()) else 0
+        assert num_experts == num_local_experts * self.world_size, "experts must split evenly over the ranks"
+        self.handle = None
+        self.topk_idx = None
+        self.topk_weights = None
+        self.hidden_shape = None
+
+    # ---- synchronous pair -------------------------------------------------------------------
+    def dispatch(self, x: Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]], topk_idx: torch.Tensor,
+                 topk_weights: torch.Tensor, expert_list: List[int] = None, previous_event=None):
+        hidden_states = x[0] if isinstance(x, tuple) else x
+        self.hidden_shape = hidden_states.shape
+        recv_x, recv_idx, recv_w, per_expert, handle, _ = self.dispatch_normal_async(
+            x, topk_idx.to(torch.int64), topk_weights, self.num_experts, previous_event, async_finish=False)
+        self.handle = handle
+        self.topk_idx = recv_idx
+        self.topk_weights = recv_w
+        return recv_x, recv_idx, recv_w, per_expert
+
+    def combine(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        out, _ = self.combine_normal_async(hidden_states, self.handle, async_finish=False)
+        self.handle = None
+        return out.view(self.hidden_shape)
+
+    # ---- async flavoured API (same stream; events mark completion) ----------------------------
+    def dispatch_normal_async(self, x, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+                              num_experts: Optional[int] = None, previous_event=None, async_finish=True):
+        if previous_event is not None:
+            previous_event.current_stream_wait()
+        x_q, x_s = x if isinstance(x, tuple) else (x, None)
+        w_sz, nle = self.world_size, self.num_local_experts
+        plan = make_normal_plan(topk_idx, w_sz, self.rank, nle, self.group, self.expert_alignment)
+        t, k = topk_idx.shape
+        dev = x_q.device
+        n_send, n_recv = plan.num_send, plan.num_recv
+        # pack: one pass over the tokens, each row copied to its (<= W) destinations
+        send_x, send_s = ops.permute_rows(x_q.view(torch.uint8) if x_q.dtype != torch.uint8 else x_q,
+                                          x_s, plan.dst_pos, w_sz, n_send)
+        # small per-row metadata: local ids and weights, packed in the same order
+        tok = torch.arange(t, device=dev)[:, None].expand(t, w_sz)
+        sel = plan.dst_pos >= 0
+        order = torch.argsort(plan.dst_pos[sel].to(torch.int64))
+        src_tok = tok[sel][order]
+        dest_rank = torch.arange(w_sz, device=dev)[None, :].expand(t, w_sz)[sel][order]
+        send_ids = localize_ids(topk_idx.to(torch.int64)[src_tok], dest_rank, nle)
+        send_w = topk_weights.to(torch.float32)[src_tok]
+        recv_x = torch.empty(n_recv, x_q.shape[1], dtype=torch.uint8, device=dev)
+        recv_ids = torch.empty(n_recv, k, dtype=torch.int64, device=dev)
+        recv_w = torch.empty(n_recv, k, dtype=torch.float32, device=dev)
+        _a2a(recv_x, send_x, plan.recv_splits, plan.send_splits, self.group, w_sz)
+        recv_s = None
+        if x_s is not None:
+            recv_s = torch.empty(n_recv, x_s.shape[1], dtype=torch.float32, device=dev)
+            _a2a(recv_s, send_s, plan.recv_splits, plan.send_splits, self.group, w_sz)
+        _a2a(recv_ids, send_ids.contiguous(), plan.recv_splits, plan.send_splits, self.group, w_sz)
+        _a2a(recv_w, send_w.contiguous(), plan.recv_splits, plan.send_splits, self.group, w_sz)
+        recv_x = recv_x.view(x_q.dtype)
+        out_x = (recv_x, recv_s) if x_s is not None else recv_x
+        handle = (plan,)
+        return out_x, recv_ids, recv_w, plan.recv_tokens_per_expert, handle, _record_event()
+
+    def combine_normal_async(self, x: torch.Tensor, handle: Tuple, previous_event=None, async_finish=True):
+        if previous_event is not None:
+            previous_event.current_stream_wait()
+        (plan,) = handle
+        w_sz = self.world_size
+        back = torch.empty(plan.num_send, x.shape[1], dtype=x.dtype, device=x.device)
+        _a2a(back, x.contiguous(), plan.send_splits, plan.recv_splits, self.group, w_sz)
+        out = torch.empty(plan.num_tokens, x.shape[1], dtype=x.dtype, device=x.device)
+        ones = torch.ones(plan.num_tokens, w_sz, dtype=torch.float32, device=x.device)
+        # out[t] = sum over the ranks the token was sent to, in rank order (fp32 accumulation)
+        ops.ep_gather(back, plan.dst_pos, ones, plan.dst_pos, out)
+        return out, _record_event()
+
+    def capture(self):
+        return _record_event()
+
+    def release(self):
+        self.handle = None
+        self.topk_idx = None
+        self.topk_weights = None
+        return True
+
+
+# ----------------------------------------------------------------------------------------------
+# low-latency (decode) mode: masked layout [E_local, max_tokens_per_rank * W, H]
+# ----------------------------------------------------------------------------------------------
+class LowLatencyPlan:
+    def __init__(self):
+        self.slot_pos = None       # int32 [T*k]: row of each (token, slot) pair in the send buffer
+        self.send_splits = None
+        self.recv_splits = None
+        self.recv_dst = None       # int32 [n_recv]: row of each received pair in the masked layout
+        self.masked_m = None       # int32 [E_local]
+        self.num_send = 0
+        self.num_recv = 0
+        self.num_tokens = 0
+
+
+def make_low_latency_plan(counts: torch.Tensor, world_size: int, rank: int, num_local_experts: int, group,
+                          rows_per_expert: int) -> LowLatencyPlan:
+    """counts: int32/int64 [E] number of (token, slot) pairs this rank routes to every global expert."""
+    dev = counts.device
+    mine = counts.to(torch.int64).view(1, -1)
+    e = mine.shape[1]
+    gathered = torch.empty(world_size, e, dtype=torch.int64, device=dev)
+    if world_size > 1:
+        dist.all_gather_into_tensor(gathered, mine, group=group)
+    else:
+        gathered.copy_(mine)
+    host = gathered.cpu()
+    plan = LowLatencyPlan()
+    per_rank = host[rank].view(world_size, num_local_experts).sum(dim=1)
+    plan.send_splits = per_rank.tolist()
+    local = host[:, rank * num_local_experts:(rank + 1) * num_local_experts]      # [W(src), E_local]
+    plan.recv_splits = local.sum(dim=1).tolist()
+    plan.num_send = int(sum(plan.send_splits))
+    plan.num_recv = int(sum(plan.recv_splits))
+    # received rows arrive grouped by source rank, inside a source sorted by local expert;
+    # the masked layout wants, per expert, the rows of source 0 first, then source 1, ...
+    before = torch.cumsum(local, dim=0) - local                                   # rows of earlier sources, per expert
+    dst = []
+    for s in range(world_size):
+        for j in range(num_local_experts):
+            c = int(local[s, j])
+            if c:
+                dst.append(torch.arange(c, dtype=torch.int32) + int(j * rows_per_expert + before[s, j]))
+    plan.recv_dst = (torch.cat(dst) if dst else torch.zeros(0, dtype=torch.int32)).to(dev)
+    plan.masked_m = local.sum(dim=0).to(torch.int32).to(dev)
+    assert int(plan.masked_m.max()) <= rows_per_expert if plan.masked_m.numel() else True, \
+        "an expert received more rows than max_tokens_per_rank * world_size"
+    return plan
+
+
+class TokenDispatcherLowLatency:
+    """`DeepEPTokenDispatcherLowLatency` of the reference (token_dispatcher.py:455-602) over NCCL."""
+
+    def __init__(self, group, num_experts: int = None, num_local_experts: int = None, hidden_size: int = None,
+                 params_dtype: torch.dtype = None, return_recv_hook: bool = False,
+                 num_max_dispatch_tokens_per_rank: int = 128):
+        import os
+        self.group = group
+        self.num_experts = num_experts
+        self.num_local_experts = num_local_experts
+        self.hidden_size = hidden_size
+        self.params_dtype = params_dtype
+        self.world_size = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if (dist.is_available() and dist.is_initialized()) else 0
+        self.num_max_dispatch_tokens_per_rank = int(os.getenv("DEEPEP_MAX_TOKENS_PER_RANK",
+                                                              str(num_max_dispatch_tokens_per_rank)))
+        self.return_recv_hook = return_recv_hook
+        self.handle = None
+
+    @property
+    def rows_per_expert(self):
+        return self.num_max_dispatch_tokens_per_rank * self.world_size
+
+    def dispatch(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+                 num_experts: int, use_fp8: bool = True):
+        if num_experts is not None and self.num_experts is not None:
+            assert self.num_experts == num_experts
+        topk_idx = topk_idx.to(torch.int64)
+        expected_m = (hidden_states.shape[0] * self.world_size * topk_idx.shape[1] + num_experts) // num_experts
+        packed, masked_m, self.handle, event, _ = self.dispatch_async(hidden_states, topk_idx, num_experts, use_fp8,
+                                                                      async_finish=False)
+        return packed, topk_idx, topk_weights, masked_m, expected_m
+
+    def dispatch_async(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, num_experts: Optional[int] = None,
+                       use_fp8: bool = True, async_finish: bool = True):
+        assert topk_idx.dtype == torch.int64
+        assert use_fp8, "the masked layout of this package is FP8"
+        assert hidden_states.shape[0] <= self.num_max_dispatch_tokens_per_rank
+        t, k = topk_idx.shape
+        h = hidden_states.shape[1]
+        dev = hidden_states.device
+        w_sz, nle, rpe = self.world_size, self.num_local_experts, self.rows_per_expert
+        # pairs sorted by global expert = send order; the quantiser writes each token's row to its k slots
+        _, _, _, pos, counts = ops.sort_by_expert(topk_idx, self.num_experts, want_pos=True, want_counts=True)
+        plan = make_low_latency_plan(counts, w_sz, self.rank, nle, self.group, rpe)
+        plan.slot_pos, plan.num_tokens = pos, t
+        send_x, send_s = ops.quant_fp8(hidden_states, 128, _C.QUANT_DIV_EPS, 1e-10, False, pos, k, plan.num_send)
+        recv_x = torch.empty(plan.num_recv, h, dtype=torch.uint8, device=dev)
+        recv_s = torch.empty(plan.num_recv, h // 128, dtype=torch.float32, device=dev)
+        _a2a(recv_x, send_x.view(torch.uint8), plan.recv_splits, plan.send_splits, self.group, w_sz)
+        _a2a(recv_s, send_s, plan.recv_splits, plan.send_splits, self.group, w_sz)
+        packed_x, packed_s = ops.permute_rows(recv_x, recv_s, plan.recv_dst, 1, nle * rpe)
+        packed = [DisposibleTensor(packed_x.view(ops.FP8).view(nle, rpe, h)),
+                  DisposibleTensor(packed_s.view(nle, rpe, h // 128))]
+        return packed, plan.masked_m, (plan,), _record_event(), (lambda: None)
+
+    def combine(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor):
+        out, _, _ = self.combine_async(hidden_states, topk_idx.to(torch.int64), topk_weights.to(torch.float32),
+                                       self.handle, async_finish=False)
+        return out
+
+    def combine_async(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+                      handle: Tuple, async_finish: bool):
+        assert topk_idx.dtype == torch.int64
+        assert topk_weights.dtype == torch.float32
+        (plan,) = handle
+        nle, rpe, h = hidden_states.shape
+        flat = hidden_states.reshape(nle * rpe, h)
+        # back to arrival order: row i of the exchange buffer is masked-layout row recv_dst[i]
+        ones = torch.ones(plan.num_recv, 1, dtype=torch.float32, device=flat.device)
+        send_back = torch.empty(plan.num_recv, h, dtype=flat.dtype, device=flat.device)
+        idx = plan.recv_dst.view(-1, 1)
+        ops.ep_gather(flat, idx, ones, idx, send_back)
+        back = torch.empty(plan.num_send, h, dtype=flat.dtype, device=flat.device)
+        _a2a(back, send_back, plan.send_splits, plan.recv_splits, self.group, self.world_size)
+        out = torch.empty(plan.num_tokens, h, dtype=flat.dtype, device=flat.device)
+        # out[t] = sum_k w[t, k] * back[slot_pos[t, k]]
+        ops.ep_gather(back, topk_idx.to(torch.int32).contiguous(), topk_weights.contiguous(),
+                      plan.slot_pos.view(plan.num_tokens, -1), out)
+        return out, _record_event(), (lambda: None)

@@ -1,0 +1,187 @@
+/*
+ * dlblas_b200 — C ABI of the B200 (sm_100a) FP8 MoE expert path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (cudaStream_t passed as void*).  The caller owns every buffer: inputs,
+ * outputs and workspaces; nothing is allocated inside a call and no pointer is
+ * kept after return.  Calls
+ * return DLB_OK (0) or a negative code; dlb_last_error_string() gives the
+ * message of the last failure on the calling thread.  Kernels are enqueued on
+ * the given stream and the calls do not synchronise.
+ *
+ * Each declaration names the interface of the reference project
+ * (DeepLink-org/DLBlas, paths relative to its root) that it stands in for.
+ */
+#ifndef DLBLAS_B200_H
+#define DLBLAS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define DLB_API __attribute__((visibility("default")))
+#else
+#define DLB_API
+#endif
+
+#define DLB_OK 0
+#define DLB_ERR_INVALID (-1)     /* bad shape, dtype, stride or alignment          */
+#define DLB_ERR_WORKSPACE (-2)   /* workspace missing or too small                 */
+#define DLB_ERR_CUDA (-3)        /* a CUDA runtime / driver call failed            */
+#define DLB_ERR_UNSUPPORTED (-4) /* device is not sm_100 or feature not built      */
+
+/* element types */
+#define DLB_F32 0
+#define DLB_BF16 1
+#define DLB_F16 2
+#define DLB_I32 3
+#define DLB_I64 4
+
+/* scale arithmetic of the 1xG quantisers */
+#define DLB_QUANT_RECIP_MUL 0 /* scale = absmax * (1/448), no epsilon  (dlblas/kernels/moe.py:398-417)  */
+#define DLB_QUANT_DIV_EPS 1   /* scale = max(absmax, eps) / 448        (dlblas/kernels/fp8.py:44-48)    */
+
+/* epilogues of the grouped GEMM */
+#define DLB_EPI_STORE 0          /* C[p, :] = cast(acc)                                          */
+#define DLB_EPI_SCATTER_WEIGHT 1 /* C[sorted_idx[p], :] = cast(acc * weights[sorted_idx[p]])     */
+#define DLB_EPI_SWIGLU_QUANT 2   /* h = silu(gate)*up with the reference's two bf16 roundings,   */
+                                 /* then 1x128 FP8 quantisation: q[p, :], q_scale[p, :]          */
+
+/* Status word written by kernels that wait on barriers (bounded waits). */
+#define DLB_STATUS_OK 0
+#define DLB_STATUS_TIMEOUT 1
+
+DLB_API int dlb_version(void);
+DLB_API const char* dlb_last_error_string(void);
+/* Number of kernels launched by this library on the calling thread since the last reset. */
+DLB_API int64_t dlb_launch_count(int reset);
+
+/* ---- token-by-expert stable sort -----------------------------------------
+ * Replaces _dlblas_get_sorted_idx + _start_end_kernel
+ * (dlblas/layers/moe/kernels/fused_moe.py:27-51, 83-88).
+ * ids: [num_slots] int32 or int64 expert ids, -1 = not routed here.
+ * sorted_idx[p] = flat slot index at sorted position p (stable: `-1` entries first,
+ * ascending flat index inside an expert).  exp_start/exp_end: int64 [num_experts],
+ * start = end = 0 for an expert without tokens.  Optional outputs (may be NULL):
+ * slot_pos[f] = sorted position p of flat slot f (int32); for a slot with id < 0 it is stored as
+ * -(p + 1) so that the permutation kernels, which skip negative destinations, move no data for it.
+ * rank_in_expert[f] = position of slot f inside its expert's segment (int32, -1 for id < 0),
+ * counts[e] (int32). */
+DLB_API size_t dlb_sort_by_expert_workspace_size(int64_t num_slots, int num_experts);
+DLB_API int dlb_sort_by_expert(const void* ids, int ids_dtype, int64_t num_slots, int num_experts,
+                       int64_t* sorted_idx, int64_t* exp_start, int64_t* exp_end, int32_t* slot_pos,
+                       int32_t* rank_in_expert, int32_t* counts, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+/* Tile list for the grouped GEMMs: tiles[0] = {num_tiles,0,0,0}, tiles[1+i] =
+ * {local expert, first row, valid rows (<= 128), 0}.  Needs room for 1 + max_tiles int4.
+ * Built on the device from exp_start/exp_end (sorted layout; replaces the E-times
+ * over-provisioned grid of fused_moe_blocked_f8_kernel,
+ * dlblas/layers/moe/kernels/blocked_fp8_fused_moe.py:69-92, 197-199) or from masked_m
+ * (masked layout [E, rows_per_expert, K] of FusedMoELowLatency, dlblas/layers/moe/ep_moe.py:199-261). */
+DLB_API int dlb_moe_build_tiles(const int64_t* exp_start, const int64_t* exp_end, int expert_offset,
+                        int num_local_experts, int32_t* tiles, int max_tiles, void* stream);
+DLB_API int dlb_moe_build_tiles_masked(const int32_t* masked_m, int num_local_experts, int rows_per_expert,
+                               int32_t* tiles, int max_tiles, void* stream);
+
+/* ---- 1xG FP8 (e4m3) quantisation -------------------------------------------
+ * Replaces quant_fp8 (dlblas/kernels/moe.py:377-474), per_token_group_quant_fp8
+ * (dlblas/kernels/fp8.py:9-182) and tma_align_input_scale (dlblas/kernels/quant_dequant.py:22-83,
+ * through the scale strides).  x: [m, k] with row stride ldx (elements).  q: [rows_out, k]
+ * e4m3, scales fp32 at scales[row * scale_row_stride + group * scale_group_stride].
+ * dst_pos == NULL: output row = input row.  Otherwise input row t is written to rows
+ * dst_pos[t * fanout + j], j < fanout (negative entries skipped): the quantiser fused
+ * with the token-by-expert permutation. */
+DLB_API int dlb_quant_fp8(const void* x, int x_dtype, int64_t m, int64_t k, int64_t ldx, int group_size, int mode,
+                  float eps, void* q, float* scales, int64_t scale_row_stride, int64_t scale_group_stride,
+                  const int32_t* dst_pos, int fanout, void* stream);
+
+/* Row permutation of already quantised rows (+ their scales): the data movement of
+ * ep_scatter (dlblas/kernels/fused_moe_v3.py:49-93) with deterministic destinations. */
+DLB_API int dlb_permute_rows(const void* q, int64_t row_bytes, const float* scales, int64_t groups, int64_t m,
+                     const int32_t* dst_pos, int fanout, void* out_q, float* out_scales, void* stream);
+
+/* ---- activation -------------------------------------------------------------
+ * silu_and_mul (dlblas/layers/moe/kernels/activation.py:17-95, dlblas/kernels/activation.py:89-131):
+ * out[r, j] = cast(silu_f32(in[r, j]) * in[r, n + j]). */
+DLB_API int dlb_silu_and_mul(const void* gate_up, int dtype, int64_t rows, int64_t n, int64_t ld_in, void* out,
+                     int64_t ld_out, void* stream);
+/* Fused silu*up + 1x128 quantisation.  round_silu != 0 rounds silu(gate) to the input
+ * dtype before the multiply (silu_and_mul_masked_post_quant_fwd, dlblas/kernels/moe.py:204-319);
+ * round_silu == 0 rounds only the product (silu_and_mul followed by quant_fp8,
+ * dlblas/layers/moe/kernels/blocked_fp8_fused_moe.py:313-315).  masked_m != NULL: input is
+ * [experts, rows_per_expert, 2n] and only rows < masked_m[e] are processed. */
+DLB_API int dlb_silu_mul_quant(const void* gate_up, int dtype, int64_t rows, int64_t n, int quant_mode, float eps,
+                       int round_silu, const int32_t* masked_m, int64_t rows_per_expert, void* q,
+                       float* scales, void* stream);
+
+/* ---- FP8 block-scaled GEMMs (tcgen05 + TMA) ----------------------------------
+ * fp8_gemm (dlblas/kernels/fp8_gemm.py:17-89): C[m,n] = sum_kb (A_kb . B_kb^T) a_s[m,kb] b_s[n/128,kb].
+ * a: [m,k] e4m3 row-major, b: [n,k] e4m3 row-major, a_s fp32 at a_s[row*a_s_row_stride + kb*a_s_kb_stride],
+ * b_s fp32 [ceil(n/128), k/128] row-major, c: [m,n] of c_dtype (DLB_BF16/F16/F32).  k % 128 == 0,
+ * n % 8 == 0.  status (may be NULL): device int set to DLB_STATUS_TIMEOUT if a bounded wait gave up. */
+DLB_API int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int64_t a_s_row_stride, int64_t a_s_kb_stride,
+                 const float* b_s, void* c, int c_dtype, int64_t m, int64_t n, int64_t k, int32_t* status,
+                 void* stream);
+
+/* Grouped GEMM over ragged expert segments; replaces fused_moe_blocked_f8_kernel + launcher
+ * (dlblas/layers/moe/kernels/blocked_fp8_fused_moe.py:30-242) and the DeepGEMM calls
+ * m_grouped_fp8_gemm_nt_contiguous / _masked (dlblas/kernels/fused_moe_v3.py:235-245,
+ * dlblas/layers/moe/ep_moe.py:180-197).  a: [rows_a, k] e4m3 in expert-contiguous order,
+ * a_s: [rows_a, k/128]; b: [experts, n, k] e4m3; b_s: [experts, n/128, k/128]; tiles from
+ * dlb_moe_build_tiles*.  Epilogues: see DLB_EPI_*.  For DLB_EPI_SWIGLU_QUANT n is the width of
+ * b (2 * intermediate, gate rows first), c receives e4m3 [rows_a, n/2] and q_scale fp32 [rows_a, n/256]. */
+DLB_API int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a, const void* b, const float* b_s,
+                         int num_local_experts, int64_t n, int64_t k, const int32_t* tiles, int max_tiles,
+                         int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
+                         const int64_t* sorted_idx, const float* weights, int32_t* status, void* stream);
+
+/* ---- combine -----------------------------------------------------------------
+ * out[t, :] = cast(sum_j y[t*top_k + j, :]) with fp32 accumulation in slot order: the
+ * `intermediate_cache2.sum(dim=1)` of dlblas/layers/moe/kernels/blocked_fp8_fused_moe.py:337.
+ * ids (may be NULL; int32/int64 [tokens*top_k]): slots whose id is outside [id_lo, id_hi) count as
+ * zero rows and are not read (the reference zero-fills them instead, :291, :317). */
+DLB_API int dlb_moe_sum_topk(const void* y, int dtype, int64_t tokens, int top_k, int64_t h, const void* ids,
+                     int ids_dtype, int64_t id_lo, int64_t id_hi, void* out, void* stream);
+/* ep_gather (dlblas/kernels/fused_moe_v3.py:159-233): out[t] = sum_j w[t,j] * in[index[t,j]] over
+ * slots with ids[t,j] >= 0, fp32 accumulation in slot order.  ids/index: int32 or int64 (idx_dtype). */
+DLB_API int dlb_ep_gather(const void* in, int dtype, int64_t h, const void* ids, const void* index, int idx_dtype,
+                  const float* weights, int64_t tokens, int top_k, void* out, void* stream);
+/* ep_scatter (dlblas/kernels/fused_moe_v3.py:19-155): expert_start_loc = exclusive cumsum of
+ * counts, m_indices[row] = expert of the row, output_index[t,j] = destination row (token-major,
+ * slot-minor order inside an expert: deterministic), rows and scales copied.  ids int32 or int64. */
+DLB_API size_t dlb_ep_scatter_workspace_size(int64_t tokens, int top_k, int num_experts);
+DLB_API int dlb_ep_scatter(const void* x, int64_t row_bytes, const float* x_scale, int64_t groups, const void* ids,
+                   int idx_dtype, int64_t tokens, int top_k, const int32_t* counts, int num_experts,
+                   int32_t* expert_start_loc, void* out_x, float* out_scale, int32_t* m_indices,
+                   int64_t m_indices_len, void* output_index, void* workspace, size_t workspace_bytes,
+                   void* stream);
+
+/* ---- routing -------------------------------------------------------------------
+ * topk(softmax(logits, fp32), k) with lowest-index tie-break, optional w / sum(w): the routing the
+ * reference's callers run in torch (tests/kernels/test_fused_moe_v2.py:100-102) + _renormalize
+ * (dlblas/layers/moe/kernels/blocked_fp8_fused_moe.py:245-250).  weights fp32 [t,k]; ids int32/int64. */
+DLB_API int dlb_route_softmax_topk(const void* logits, int dtype, int64_t tokens, int experts, int top_k,
+                           int renormalize, float* weights, void* ids, int ids_dtype, void* stream);
+/* biased_grouped_topk (dlblas/kernels/moe.py:477-521): sigmoid scores + bias, group score = top-2 sum,
+ * keep topk_group groups, top-k inside, weights = unbiased scores (renormalised on request).
+ * Slots come out in descending biased score, ties to the lowest index. */
+DLB_API int dlb_route_grouped_topk(const void* logits, int dtype, const float* bias, int64_t tokens, int experts,
+                           int num_groups, int topk_group, int top_k, int renormalize, float* weights,
+                           int32_t* ids, void* stream);
+/* dlblas.topk_gating forward (dlblas/__init__.py:15-25, dlblas/kernels/topk_gating.py:245-268 and the
+ * part1/2/3 kernels): capacity-limited softmax top-k gating.  Outputs: l_aux (1 element, logits dtype),
+ * ec_idx int32 [k*t] (k-major), gate weights [k*t] (logits dtype), select int64 [experts*capacity]. */
+DLB_API size_t dlb_topk_gating_workspace_size(int64_t tokens, int experts, int top_k);
+DLB_API int dlb_topk_gating(const void* logits, int dtype, int64_t tokens, int experts, int top_k, int64_t capacity,
+                    void* l_aux, int32_t* ec_idx, void* gate_weights, int64_t* select, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DLBLAS_B200_H */
