@@ -1,0 +1,427 @@
+"""Benchmark of the FP8 MoE expert path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--tokens T]
+
+Workload ("step" = one MoE layer forward over one batch of synthetic tokens): the
+DeepSeek-V3-shaped prefill layer of the benchmark set — 8192 tokens per GPU, hidden 7168,
+expert intermediate 2048, 256 routed experts top-8 with grouped routing (8 groups, 4 kept,
+sigmoid scores + N(0, 0.01^2) bias), one shared expert, FP8 e4m3 weights with 128x128 block
+scales, bf16 in/out.  With N > 1 GPUs the layer runs expert-parallel (256 / N experts per rank,
+8192 tokens per rank: weak scaling) with the NCCL dispatch / combine of this package.
+
+One JSON line is printed by rank 0.  `value` = tokens/s with inputs resident in HBM, `e2e` = the
+same through host buffers (pinned host -> device copy of the step's inputs and device -> host
+read of the result inside the timed region).  `--impl reference` times the CPU restatement of
+the reference path (oracle/) on the host cores on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+T_PER_GPU, H, INTER, E, TOPK, GROUPS, TOPK_GROUP = 8192, 7168, 2048, 256, 8, 8, 4
+FP8 = torch.float8_e4m3fn
+METRIC = "moe_layer_tokens_per_s"
+WORKLOAD = "deepseek_v3_moe_prefill"
+
+
+def layer_flops(tokens: int) -> float:
+    return 6.0 * tokens * TOPK * H * INTER + 6.0 * tokens * H * INTER     # routed + shared expert
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------------------------
+# synthetic inputs
+# --------------------------------------------------------------------------------------------
+def quantize_blocks_gpu(w: torch.Tensor):
+    e, n, k = w.shape
+    blk = w.view(e, n // 128, 128, k // 128, 128)
+    s = blk.abs().amax(dim=(2, 4), keepdim=True) / 448.0
+    q = (blk / s).clamp_(-448.0, 448.0).view(e, n, k).to(FP8)
+    return q, s.view(e, n // 128, k // 128).float()
+
+
+def make_weights(num_experts: int, seed: int, dev, chunk: int = 8):
+    """Random-init expert weights ~ N(0, 0.02^2), quantised per 128x128 block (generated on the
+    device in chunks: the full fp32 tensors would not fit in host memory)."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    w13 = torch.empty(num_experts, 2 * INTER, H, dtype=FP8, device=dev)
+    w13s = torch.empty(num_experts, 2 * INTER // 128, H // 128, dtype=torch.float32, device=dev)
+    w2 = torch.empty(num_experts, H, INTER, dtype=FP8, device=dev)
+    w2s = torch.empty(num_experts, H // 128, INTER // 128, dtype=torch.float32, device=dev)
+    for e0 in range(0, num_experts, chunk):
+        n = min(chunk, num_experts - e0)
+        a = torch.randn(n, 2 * INTER, H, generator=g, device=dev) * 0.02
+        w13[e0:e0 + n], w13s[e0:e0 + n] = quantize_blocks_gpu(a)
+        b = torch.randn(n, H, INTER, generator=g, device=dev) * 0.02
+        w2[e0:e0 + n], w2s[e0:e0 + n] = quantize_blocks_gpu(b)
+        del a, b
+    return w13, w13s, w2, w2s
+
+
+def make_tokens(tokens: int, seed: int):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(tokens, H, generator=g).to(torch.bfloat16)
+    logits = torch.randn(tokens, E, generator=g)
+    bias = torch.randn(E, generator=torch.Generator().manual_seed(1234)) * 0.01
+    return x, logits, bias
+
+
+# --------------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples `nvidia-smi` every 50 ms in the background; stop(t0, t1) keeps the samples whose
+    timestamp falls inside the timed region [t0, t1] (wall clock)."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "50", "-i", str(self.gpu)], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self, t0: float, t1: float):
+        import datetime
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        rows = []
+        for line in open(self.path):
+            f = [c.strip() for c in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[1]), float(f[2]), f[5:9]))
+            except ValueError:
+                continue
+        os.unlink(self.path)
+        inside = [r for r in rows if t0 - 0.05 <= r[0] <= t1 + 0.05] or rows[-3:]
+        reasons = set()
+        for r in inside:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if inside:
+            sm = sorted(r[1] for r in inside)
+            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(r[2] for r in inside), reasons=sorted(reasons),
+                       samples=len(inside))
+        return out
+
+
+# --------------------------------------------------------------------------------------------
+# reference arm: CPU restatement on the host cores
+# --------------------------------------------------------------------------------------------
+def cpu_sample(sample_tokens: int, w_cpu, x, logits, bias):
+    """One pass of the oracle over `sample_tokens` tokens of the workload; returns seconds."""
+    from oracle import moe_oracle as O
+    w13, w13s, w2, w2s, sw13, sw13s, sw2, sw2s = w_cpu
+    xs, lg = x[:sample_tokens], logits[:sample_tokens]
+    t0 = time.perf_counter()
+    w, ids = O.biased_grouped_topk(lg, bias, TOPK, True, GROUPS, TOPK_GROUP)
+    out = O.moe_layer(xs, w, ids.long(), w13, w13s, w2, w2s, top_k=TOPK)
+    out = out + O.dense_swiglu_mlp(xs, sw13, sw13s, sw2, sw2s)
+    return time.perf_counter() - t0, out
+
+
+def cpu_weights(dev_weights=None, seed=0):
+    """fp8 weights on the host: copied back from the device arm's tensors when given, otherwise
+    generated on the host for the hit experts only is not possible up front, so all are generated
+    in chunks (bf16-free, ~11 GB of e4m3)."""
+    if dev_weights is not None:
+        return [w.cpu() for w in dev_weights]
+    g = torch.Generator().manual_seed(seed)
+    from oracle import moe_oracle as O
+    w13 = torch.empty(E, 2 * INTER, H, dtype=FP8)
+    w13s = torch.empty(E, 2 * INTER // 128, H // 128)
+    w2 = torch.empty(E, H, INTER, dtype=FP8)
+    w2s = torch.empty(E, H // 128, INTER // 128)
+    for e in range(E):
+        w13[e:e + 1], w13s[e:e + 1] = O.quantize_weight_blocks(torch.randn(1, 2 * INTER, H, generator=g) * 0.02)
+        w2[e:e + 1], w2s[e:e + 1] = O.quantize_weight_blocks(torch.randn(1, H, INTER, generator=g) * 0.02)
+    sw13, sw13s = O.quantize_weight_blocks(torch.randn(1, 2 * INTER, H, generator=g) * 0.02)
+    sw2, sw2s = O.quantize_weight_blocks(torch.randn(1, H, INTER, generator=g) * 0.02)
+    return [w13, w13s, w2, w2s, sw13[0], sw13s[0], sw2[0], sw2s[0]]
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sample = args.cpu_tokens
+    x, logits, bias = make_tokens(sample, 100)
+    w_cpu = cpu_weights(None, 0)
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, _ = cpu_sample(sample, w_cpu, x, logits, bias)
+        if i >= args.warmup:
+            times.append(dt)
+    total = sum(times)
+    tps = sample * len(times) / total
+    line = {
+        "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "impl": "reference",
+        "config": {"workload": WORKLOAD, "tokens_per_gpu": T_PER_GPU, "hidden": H, "intermediate": INTER,
+                   "experts": E, "top_k": TOPK, "shared_experts": 1},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{sample} tokens of the workload per step through oracle/moe_oracle.py "
+                                   f"(torch CPU restatement of the reference path)"},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------
+# B200 arm
+# --------------------------------------------------------------------------------------------
+class Layer:
+    """The benchmarked layer on one rank: routing + routed experts + shared expert."""
+
+    def __init__(self, world: int, rank: int, dev, group):
+        from dlblas_b200.layers.moe.ep_moe import FusedMoENormal
+        self.world, self.rank, self.dev = world, rank, dev
+        self.e_local = E // world
+        w13, w13s, w2, w2s = make_weights(self.e_local + 1, 1000 + rank, dev)    # last one = shared expert
+        self.weights = (w13, w13s, w2, w2s)
+        self.ep = None
+        if world > 1:
+            self.ep = FusedMoENormal(world, group, E, H, top_k=TOPK, out_dtype=torch.bfloat16)
+            self.side = torch.cuda.Stream(device=dev)
+        self.shared_col_ids = torch.full((T_PER_GPU, 1), self.e_local, dtype=torch.int64, device=dev)
+        self.shared_col_w = torch.ones(T_PER_GPU, 1, dtype=torch.float32, device=dev)
+
+    def step(self, x, logits, bias):
+        from dlblas_b200 import _C, ops
+        from dlblas_b200.kernels.fp8 import per_token_group_quant_fp8
+        from dlblas_b200.layers.moe.kernels.blocked_fp8_fused_moe import moe_expert_forward
+        w13, w13s, w2, w2s = self.weights
+        t = x.shape[0]
+        w, ids = ops.route_grouped_topk(logits, bias, TOPK, True, GROUPS, TOPK_GROUP)
+        if self.world == 1:
+            # the shared expert rides along as expert number E with weight 1 for every token
+            ids9 = torch.cat([ids.long(), self.shared_col_ids[:t]], dim=1)
+            w9 = torch.cat([w, self.shared_col_w[:t]], dim=1)
+            return moe_expert_forward(x, None, None, w13, w13s, w2, w2s, w9, ids9, TOPK + 1, torch.bfloat16, 0,
+                                      self.e_local + 1)
+        nl = self.e_local
+        cur = torch.cuda.current_stream()
+        self.side.wait_stream(cur)
+        with torch.cuda.stream(self.side):           # shared expert on the local tokens, beside the exchange
+            xq, xs = ops.quant_fp8(x, 128, _C.QUANT_RECIP_MUL, 0.0)
+            c1 = ops.fp8_gemm(xq, w13[nl], xs, w13s[nl], torch.bfloat16)
+            hq, hs = ops.silu_mul_quant(c1, _C.QUANT_RECIP_MUL)
+            shared = ops.fp8_gemm(hq, w2[nl], hs, w2s[nl], torch.bfloat16)
+        routed = self.ep.forward(x, w, ids.long(), w13[:nl], w13s[:nl], w2[:nl], w2s[:nl])
+        cur.wait_stream(self.side)
+        return routed.add_(shared)
+
+
+def time_steps(fn, steps, dev):
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize(dev)
+    return start.elapsed_time(end)
+
+
+def run_b200(args):
+    import torch.distributed as dist
+
+    from dlblas_b200 import _C, ops
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    tokens = args.tokens
+    layer = Layer(world, rank, dev, group)
+    x_h, logits_h, bias_h = make_tokens(tokens, 100 + rank)
+    x_pin, logits_pin = x_h.pin_memory(), logits_h.pin_memory()
+    out_pin = torch.empty(tokens, H, dtype=torch.bfloat16).pin_memory()
+    x_d, logits_d, bias_d = x_h.to(dev), logits_h.to(dev), bias_h.to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def step_resident():
+        return layer.step(x_d, logits_d, bias_d)
+
+    def step_e2e():
+        x_d.copy_(x_pin, non_blocking=True)
+        logits_d.copy_(logits_pin, non_blocking=True)
+        out = layer.step(x_d, logits_d, bias_d)
+        out_pin.copy_(out, non_blocking=True)
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    _C.check_status(dev)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        for _ in range(3):
+            step_resident()          # the sampler needs a moment to come up
+        time.sleep(0.3)
+    barrier()
+    _C.launch_count(reset=True)
+    wall0 = time.time()
+    ms = time_steps(step_resident, args.steps, dev)
+    wall1 = time.time()
+    launches = _C.launch_count(reset=True)
+    barrier()
+    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    ms_e2e = time_steps(step_e2e, args.steps, dev)
+    barrier()
+    _C.check_status(dev)
+    if world > 1:
+        tmax = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(tmax[0]), float(tmax[1])
+
+    # ---- dominant kernel: the w13 grouped GEMM with the fused silu*up + quantisation epilogue ----
+    roof = None
+    cpu_base = None
+    if rank == 0:
+        peaks = load_peaks()
+        e_loc = layer.e_local + (1 if world == 1 else 0)
+        w13, w13s, w2, w2s = layer.weights
+        w_r, ids_r = ops.route_grouped_topk(logits_d, bias_d, TOPK, True, GROUPS, TOPK_GROUP)
+        if world == 1:
+            ids_k = torch.cat([ids_r.long(), layer.shared_col_ids[:tokens]], dim=1)
+            k_eff = TOPK + 1
+        else:
+            # single-rank stand-in for the received tokens: this rank's share of the routed slots
+            mine = (ids_r >= rank * layer.e_local) & (ids_r < (rank + 1) * layer.e_local)
+            ids_k = torch.where(mine, ids_r - rank * layer.e_local, torch.full_like(ids_r, -1)).long()
+            k_eff = TOPK
+        s_rows = tokens * k_eff
+        sidx, st, en, pos = ops.sort_by_expert(ids_k, e_loc, want_pos=True)
+        mt = ops.max_tiles_for(s_rows, e_loc)
+        tiles = ops.build_tiles(st, en, 0, e_loc, mt)
+        a1, a1s = ops.quant_fp8(x_d, 128, _C.QUANT_RECIP_MUL, 0.0, False, pos, k_eff, s_rows)
+        hq = torch.empty(s_rows, INTER, dtype=FP8, device=dev)
+        hs = torch.empty(s_rows, INTER // 128, dtype=torch.float32, device=dev)
+        routed_rows = int((ids_k >= 0).sum())
+
+        def gemm1():
+            ops.grouped_gemm(a1, a1s, w13[:e_loc], w13s[:e_loc], tiles, mt, _C.EPI_SWIGLU_QUANT, hq, q_scale=hs,
+                             round_dtype=torch.bfloat16)
+
+        for _ in range(3):
+            gemm1()
+        kms = time_steps(gemm1, max(args.steps, 5), dev) / max(args.steps, 5)
+        flops = 2.0 * routed_rows * (2 * INTER) * H
+        achieved = flops / (kms * 1e-3) / 1e12
+        fp8_peak = 2.0 * peaks["bf16_tflops"]
+        roof = {"kernel": "gemm_fp8_kernel<256, SWIGLU_QUANT> (w13 grouped GEMM)", "bound": "tensor",
+                "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
+                "traffic": None, "ms_per_launch": kms,
+                "peak_note": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TFLOP/s): "
+                             f"e4m3 tensor rate is twice bf16 on B200; no FP8 figure is measured on this pool"}
+        if not args.no_cpu:
+            torch.set_num_threads(os.cpu_count() or 1)
+            if world == 1:
+                w_cpu = [w13[:E].cpu(), w13s[:E].cpu(), w2[:E].cpu(), w2s[:E].cpu(), w13[E].cpu(), w13s[E].cpu(),
+                         w2[E].cpu(), w2s[E].cpu()]
+                dt, ref_out = cpu_sample(args.cpu_tokens, w_cpu, x_h, logits_h, bias_h)
+                got = layer.step(x_d[:args.cpu_tokens].contiguous(), logits_d[:args.cpu_tokens].contiguous(), bias_d)
+                from oracle import moe_oracle as O
+                err = O.rel_frobenius(got.cpu(), ref_out)
+                cpu_base = {"value": args.cpu_tokens / dt, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                            "kind": "port", "sample": f"first {args.cpu_tokens} tokens of the step's batch, all "
+                            f"experts they hit, through oracle/moe_oracle.py", "rel_frobenius_vs_gpu": err}
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        total_tokens = tokens * world
+        tps = total_tokens * args.steps / (ms * 1e-3)
+        tps_e2e = total_tokens * args.steps / (ms_e2e * 1e-3)
+        tflops = layer_flops(total_tokens) * args.steps / (ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "tokens_per_gpu": tokens, "hidden": H, "intermediate": INTER,
+                       "experts": E, "top_k": TOPK, "shared_experts": 1, "routing": "grouped 8/4 sigmoid+bias",
+                       "parallelism": f"ep{world}",
+                       "l2": "inputs larger than L2: every step streams this rank's expert weights "
+                             f"({(layer.e_local + 1) * 3 * H * INTER / 1e9:.2f} GB) from HBM"},
+            "tflops": tflops, "fp8_peak_frac": tflops / (2.0 * load_peaks()["bf16_tflops_sustained"] * world),
+            "e2e": {"value": tps_e2e, "unit": "tokens/s", "h2d_bytes_per_step": tokens * H * 2 + tokens * E * 4,
+                    "d2h_bytes_per_step": tokens * H * 2, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches, "clocks": clocks, "roofline": roof,
+        }
+        if cpu_base is not None:
+            line["cpu_baseline"] = cpu_base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--tokens", type=int, default=T_PER_GPU, help="tokens per GPU per step")
+    ap.add_argument("--cpu-tokens", type=int, default=32, help="tokens of the CPU baseline sample")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -99,24 +99,26 @@ class FusedMoELowLatency:
     def experts(self, hidden_states_fp8, gate_up_weight: torch.Tensor, gate_up_scale: torch.Tensor,
                 gate_down_weight: torch.Tensor, gate_down_scale: torch.Tensor, masked_m: torch.Tensor,
                 expected_m: int):
-        x_q = DisposibleTensor.maybe_unwrap(hidden_states_fp8[0])
-        x_s = DisposibleTensor.maybe_unwrap(hidden_states_fp8[1])
-        num_groups, m, k = x_q.shape
+        num_groups, m, k = hidden_states_fp8[0].shape
+        dev = hidden_states_fp8[0].device
         n = gate_up_weight.size(1)
         mm = masked_m if masked_m.dtype == torch.int32 else masked_m.to(torch.int32)
         tiles, max_tiles = ops.build_tiles_masked(mm, m)
-        gateup_output = torch.empty((num_groups, m, n), device=x_q.device, dtype=self.out_dtype)
-        ops.grouped_gemm(x_q.view(num_groups * m, k), x_s.reshape(num_groups * m, -1).contiguous(), gate_up_weight,
+        gateup_output = torch.empty((num_groups, m, n), device=dev, dtype=self.out_dtype)
+        ops.grouped_gemm(DisposibleTensor.maybe_unwrap(hidden_states_fp8[0]).view(num_groups * m, k),
+                         DisposibleTensor.maybe_unwrap(hidden_states_fp8[1]).view(num_groups * m, -1), gate_up_weight,
                          gate_up_scale, tiles, max_tiles, _C.EPI_STORE, gateup_output.view(num_groups * m, n))
+        # the dispatch buffers are the largest tensors of the decode step: free them as early as the
+        # reference does (kernels already enqueued keep the memory alive through the caching allocator)
         DisposibleTensor.maybe_dispose(hidden_states_fp8[0])
         DisposibleTensor.maybe_dispose(hidden_states_fp8[1])
-        down_input = torch.empty((num_groups, m, n // 2), device=x_q.device, dtype=gate_down_weight.dtype)
-        down_input_scale = torch.empty((num_groups, m, n // 2 // self.block_size), device=x_q.device,
+        down_input = torch.empty((num_groups, m, n // 2), device=dev, dtype=gate_down_weight.dtype)
+        down_input_scale = torch.empty((num_groups, m, n // 2 // self.block_size), device=dev,
                                        dtype=torch.float32)
         silu_and_mul_masked_post_quant_fwd(gateup_output, down_input, down_input_scale, self.block_size, mm)
         del gateup_output
         n2 = gate_down_weight.size(1)
-        down_output = torch.empty((num_groups, m, n2), device=x_q.device, dtype=self.out_dtype)
+        down_output = torch.empty((num_groups, m, n2), device=dev, dtype=self.out_dtype)
         ops.grouped_gemm(down_input.view(num_groups * m, n // 2), down_input_scale.view(num_groups * m, -1),
                          gate_down_weight, gate_down_scale, tiles, max_tiles, _C.EPI_STORE,
                          down_output.view(num_groups * m, n2))
