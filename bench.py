@@ -407,8 +407,56 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_profile(args):
+    """Small stand-alone case of one kernel for `ncu` (a few GB on the device, a handful of
+    launches): `--profile gemm1|gemm2|dense` with `--tokens` and `--experts` scaled down so that
+    rows per expert (tokens * 8 / experts) stay at the full workload's 256."""
+    from dlblas_b200 import _C, ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    e, t = args.experts, args.tokens
+    g = torch.Generator().manual_seed(7)
+    if args.profile == "dense":
+        m, n, k = t, 2 * INTER, H
+        a = (torch.randn(m, k, generator=g)).to(FP8).to(dev)
+        b = (torch.randn(n, k, generator=g)).to(FP8).to(dev)
+        a_s = torch.rand(m, k // 128, generator=g).to(dev)
+        b_s = torch.rand(n // 128, k // 128, generator=g).to(dev)
+        for _ in range(args.steps):
+            ops.fp8_gemm(a, b, a_s, b_s, torch.bfloat16)
+        torch.cuda.synchronize()
+        _C.check_status(dev)
+        return
+    w13, w13s, w2, w2s = make_weights(e, 1, dev)
+    x = torch.randn(t, H, generator=g).to(torch.bfloat16).to(dev)
+    ids = torch.stack([torch.randperm(e, generator=g)[:TOPK] for _ in range(t)]).to(dev)
+    wts = torch.rand(t, TOPK, generator=g).to(dev)
+    s_rows = t * TOPK
+    sidx, st, en, pos = ops.sort_by_expert(ids, e, want_pos=True)
+    mt = ops.max_tiles_for(s_rows, e)
+    tiles = ops.build_tiles(st, en, 0, e, mt)
+    a1, a1s = ops.quant_fp8(x, 128, _C.QUANT_RECIP_MUL, 0.0, False, pos, TOPK, s_rows)
+    hq = torch.empty(s_rows, INTER, dtype=FP8, device=dev)
+    hs = torch.empty(s_rows, INTER // 128, dtype=torch.float32, device=dev)
+    y = torch.empty(s_rows, H, dtype=torch.bfloat16, device=dev)
+    for _ in range(args.steps):
+        if args.profile == "gemm1":
+            ops.grouped_gemm(a1, a1s, w13, w13s, tiles, mt, _C.EPI_SWIGLU_QUANT, hq, q_scale=hs,
+                             round_dtype=torch.bfloat16)
+        else:
+            if _ == 0:
+                ops.grouped_gemm(a1, a1s, w13, w13s, tiles, mt, _C.EPI_SWIGLU_QUANT, hq, q_scale=hs,
+                                 round_dtype=torch.bfloat16)
+            ops.grouped_gemm(hq, hs, w2, w2s, tiles, mt, _C.EPI_SCATTER_WEIGHT, y, sorted_idx=sidx, weights=wts)
+    torch.cuda.synchronize()
+    _C.check_status(dev)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--profile", default="", choices=["", "gemm1", "gemm2", "dense"],
+                    help="run only one kernel on a small case (for ncu) and exit")
+    ap.add_argument("--experts", type=int, default=32, help="experts of the --profile case")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
@@ -417,7 +465,9 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=32, help="tokens of the CPU baseline sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile:
+        run_profile(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)
