@@ -31,6 +31,8 @@ SIGNATURES = {
     "dlb_launch_count": (c_i64, [c_int]),
     "dlb_sort_by_expert_workspace_size": (c_sz, [c_i64, c_int]),
     "dlb_sort_by_expert": (c_int, [c_vp, c_int, c_i64, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "dlb_sort_by_expert_static_capacity": (c_sz, []),
+    "dlb_sort_by_expert_static": (c_int, [c_vp, c_int, c_i64, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "dlb_moe_build_tiles": (c_int, [c_vp, c_vp, c_int, c_int, c_vp, c_int, c_vp]),
     "dlb_moe_build_tiles_masked": (c_int, [c_vp, c_int, c_int, c_vp, c_int, c_vp]),
     "dlb_quant_fp8": (c_int, [c_vp, c_int, c_i64, c_i64, c_i64, c_int, c_int, c_f, c_vp, c_vp, c_i64, c_i64, c_vp,

@@ -11,6 +11,8 @@
 //   scan:    exclusive prefix over chunks per bucket, then over buckets
 //   scatter: position = bucket base + chunk prefix + rank inside the chunk
 // Small inputs run all three phases in one CTA with the histograms in shared memory.
+#include <mutex>
+
 #include "common.cuh"
 #include "sort.cuh"
 
@@ -374,6 +376,61 @@ extern "C" int dlb_sort_by_expert(const void* ids, int ids_dtype, int64_t num_sl
   return sort_by_expert(ids, ids_dtype, num_slots, num_experts, reinterpret_cast<long long*>(sorted_idx),
                         reinterpret_cast<long long*>(exp_start), reinterpret_cast<long long*>(exp_end), slot_pos,
                         rank_in_expert, counts, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+// ---- variant of the sort that never allocates -----------------------------------------
+// Some callers cannot hand over a workspace: an inference engine that reserved all device
+// memory for its own pool at start-up has nothing left for cudaMalloc to give, and code that
+// runs where an allocation's implicit device-wide synchronisation is not acceptable must not
+// call the allocator at all.  For them the chunk histograms live in a fixed array that is
+// part of the loaded module (every GPU that loads the library holds these bytes until exit).
+namespace {
+constexpr size_t STATIC_SCRATCH_BYTES = (size_t)4 * 1024 * 1024 + 16 * 1024;
+static __device__ __align__(256) unsigned char g_sort_scratch[STATIC_SCRATCH_BYTES];
+
+// In host code `g_sort_scratch` is only a handle for the runtime, not a device address; the
+// address the kernels need is looked up once per device, with that device current.
+void* g_scratch_ptr[64] = {};
+std::mutex g_scratch_mutex;
+
+int static_scratch(void** out) {
+  int dev = 0;
+  int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  if (rc != DLB_OK) return rc;
+  DLB_REQUIRE(dev >= 0 && dev < 64, DLB_ERR_UNSUPPORTED, "sort_by_expert_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    rc = check_cuda(cudaGetSymbolAddress(&p, g_sort_scratch), "cudaGetSymbolAddress(g_sort_scratch)");
+    if (rc != DLB_OK) return rc;
+    DLB_REQUIRE(p != nullptr, DLB_ERR_CUDA, "sort_by_expert_static: the scratch array has no device address");
+    g_scratch_ptr[dev] = p;
+  }
+  *out = g_scratch_ptr[dev];
+  return DLB_OK;
+}
+}  // namespace
+
+extern "C" size_t dlb_sort_by_expert_static_capacity(void) { return STATIC_SCRATCH_BYTES; }
+
+extern "C" int dlb_sort_by_expert_static(const void* ids, int ids_dtype, int64_t num_slots, int num_experts,
+                                         int64_t* sorted_idx, int64_t* exp_start, int64_t* exp_end,
+                                         int32_t* slot_pos, int32_t* rank_in_expert, int32_t* counts, void* stream) {
+  DLB_REQUIRE(num_slots >= 0 && num_experts > 0, DLB_ERR_INVALID,
+              "sort_by_expert_static: bad sizes num_slots=%lld num_experts=%d", (long long)num_slots, num_experts);
+  const size_t need = num_slots > 0 ? sort_workspace_size(num_slots, num_experts) : 0;
+  DLB_REQUIRE(need <= STATIC_SCRATCH_BYTES, DLB_ERR_WORKSPACE,
+              "sort_by_expert_static: num_slots=%lld with num_experts=%d needs %zu bytes of scratch, the built-in "
+              "array holds %zu; use dlb_sort_by_expert with a caller-provided workspace",
+              (long long)num_slots, num_experts, need, STATIC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  int rc = static_scratch(&scratch);
+  if (rc != DLB_OK) return rc;
+  // Every word of the scratch that the kernels read is written earlier in the same call (the
+  // count kernel fills the whole histogram matrix), so leftovers of a previous call are harmless.
+  return sort_by_expert(ids, ids_dtype, num_slots, num_experts, reinterpret_cast<long long*>(sorted_idx),
+                        reinterpret_cast<long long*>(exp_start), reinterpret_cast<long long*>(exp_end), slot_pos,
+                        rank_in_expert, counts, scratch, STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
 }
 
 extern "C" int dlb_moe_build_tiles(const int64_t* exp_start, const int64_t* exp_end, int expert_offset,

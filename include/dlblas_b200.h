@@ -77,6 +77,26 @@ DLB_API int dlb_sort_by_expert(const void* ids, int ids_dtype, int64_t num_slots
                        int32_t* rank_in_expert, int32_t* counts, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* Same sort for callers that cannot allocate device memory (no counterpart in the reference).
+ * A serving engine that has handed all device memory to its own pool at start-up, or a latency-
+ * critical path that must never trigger the allocator's device-wide synchronisation, has no
+ * workspace to pass and cannot create one.  This variant keeps the chunk histograms in a fixed
+ * array inside the library image (dlb_sort_by_expert_static_capacity() bytes, about 4 MiB, held on
+ * every GPU that loads the library until the process exits) and allocates nothing, neither directly
+ * nor through a library.  Inputs and outputs are the caller's, as above.
+ *  - Limit: fails with DLB_ERR_WORKSPACE when dlb_sort_by_expert_workspace_size(num_slots,
+ *    num_experts) exceeds the capacity (only beyond about 1000 experts together with a few hundred
+ *    thousand slots; every size at 256 experts fits); use the variant with a workspace then.
+ *  - The first call on each device looks up the array's device address; make that call before any
+ *    stream capture starts on that device.
+ *  - All calls on a device share the one array: calls whose kernels may overlap on the GPU
+ *    (different streams, no dependency) race on it and give wrong results; order them.  Nothing
+ *    needs to be cleared between calls: each call overwrites every word it later reads. */
+DLB_API size_t dlb_sort_by_expert_static_capacity(void);
+DLB_API int dlb_sort_by_expert_static(const void* ids, int ids_dtype, int64_t num_slots, int num_experts,
+                              int64_t* sorted_idx, int64_t* exp_start, int64_t* exp_end, int32_t* slot_pos,
+                              int32_t* rank_in_expert, int32_t* counts, void* stream);
+
 /* Tile list for the grouped GEMMs: tiles[0] = {num_tiles,0,0,0}, tiles[1+i] =
  * {local expert, first row, valid rows (<= 128), 0}.  Needs room for 1 + max_tiles int4.
  * Built on the device from exp_start/exp_end (sorted layout; replaces the E-times
