@@ -11,7 +11,8 @@ import threading
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-SO_PATH = os.path.join(_HERE, "_dlblas_b200.so")
+# DLBLAS_B200_LIB overrides the location of the shared library (e.g. an out-of-tree build)
+SO_PATH = os.environ.get("DLBLAS_B200_LIB") or os.path.join(_HERE, "_dlblas_b200.so")
 
 DLB_F32, DLB_BF16, DLB_F16, DLB_I32, DLB_I64 = 0, 1, 2, 3, 4
 QUANT_RECIP_MUL, QUANT_DIV_EPS = 0, 1

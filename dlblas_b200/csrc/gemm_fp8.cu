@@ -9,12 +9,18 @@
 //                       acc += partial * a_scale[row, kb] * b_scale[nblk, kb] on the CUDA
 //                       cores (the scales are arbitrary fp32, so the hardware block-scale
 //                       path, which wants UE8M0 scales, does not apply), then the epilogue.
+//   warps 10-11         idle; they complete the third warpgroup so that it can hand its
+//                       registers to the promotion warpgroups (setmaxnreg).
+//
+// Register budget: an accumulator tile is 128 x BN fp32 = half of the register file at
+// BN = 256, and hiding the TMEM load latency needs 64 more staging registers per promotion
+// thread, so the promotion warpgroups run at 232 registers and the third warpgroup at 40.
 //
 // The arithmetic follows dlblas/kernels/fp8_gemm.py:50-59 and
 // dlblas/layers/moe/kernels/blocked_fp8_fused_moe.py:95-156 of the reference: fp32
 // accumulation over K blocks in increasing order, one rounding to the output type.
 //
-// All mbarrier waits are bounded: a wait that exceeds its time limit raises a CTA-wide
+// All mbarrier waits are bounded (about 2 s of SM clock cycles): a wait that exceeds its limit raises a CTA-wide
 // abort flag, every role leaves its loop, the status word is set to DLB_STATUS_TIMEOUT
 // and the kernel returns after draining what it issued.
 #include <cuda.h>
@@ -30,7 +36,9 @@ constexpr int A_STAGE_BYTES = BM * BK;
 constexpr int EPI_WARPS = 8;         // two warpgroups
 constexpr int PRODUCER_WARP = 8;
 constexpr int MMA_WARP = 9;
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 384;      // three warpgroups
+constexpr int REGS_PROMOTION = 232;    // 256 * 232 + 128 * 40 = 384 * 168
+constexpr int REGS_OTHER = 40;
 constexpr int TMEM_COLS = 512;
 
 struct GemmArgs {
@@ -49,7 +57,7 @@ struct GemmArgs {
   const long long* sorted_idx;
   const float* weights;
   int* status;
-  unsigned long long timeout_ns;
+  unsigned long long timeout_cycles;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------
@@ -64,30 +72,36 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One poll of the barrier.  The suspend-time hint lets the hardware park the warp until the
+// phase completes (or the hint, in ns, runs out) instead of spinning: a spinning role would
+// take issue slots from the promotion warps that share its scheduler.
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(1000000u)
       : "memory");
   return ok;
 }
 // Bounded wait.  Returns false when the CTA is aborting (set by this or another thread).
+// The time limit is counted in SM clock cycles (clock64 is a register read; the global
+// nanosecond timer costs hundreds of cycles per read and these waits sit on the critical path
+// of every K block).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned long long limit_ns) {
+                                          unsigned long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t polls = 0;
+  long long t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++polls & 0xffu) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > limit_ns) {
-        *abort_flag = 1;
-        return false;
-      }
+    if (*abort_flag) return false;
+    const long long now = clock64();
+    if (t0 == 0) {
+      t0 = now;
+    } else if ((unsigned long long)(now - t0) > limit_cycles) {
+      *abort_flag = 1;
+      return false;
     }
   }
   return true;
@@ -98,6 +112,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
       : "memory");
+}
+
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -117,23 +142,57 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint
       : "memory");
 }
 
-// 32 lanes x 16 consecutive columns, one fp32 per register.
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+// 32 lanes x 32 consecutive columns, one fp32 per register.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
       : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr)
       : "memory");
 }
-// Waits for this thread's outstanding tcgen05.ld.  The staging registers are listed as
+// Waits for all of this thread's outstanding tcgen05.ld.  Both staging buffers are listed as
 // read-write operands so the compiler cannot schedule arithmetic on them above the wait.
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[16]) {
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[32], uint32_t (&b)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
-                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+               : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
+                 "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]),
+                 "+r"(a[16]), "+r"(a[17]), "+r"(a[18]), "+r"(a[19]), "+r"(a[20]), "+r"(a[21]), "+r"(a[22]),
+                 "+r"(a[23]), "+r"(a[24]), "+r"(a[25]), "+r"(a[26]), "+r"(a[27]), "+r"(a[28]), "+r"(a[29]),
+                 "+r"(a[30]), "+r"(a[31]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]),
+                 "+r"(b[6]), "+r"(b[7]), "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]),
+                 "+r"(b[14]), "+r"(b[15]), "+r"(b[16]), "+r"(b[17]), "+r"(b[18]), "+r"(b[19]), "+r"(b[20]),
+                 "+r"(b[21]), "+r"(b[22]), "+r"(b[23]), "+r"(b[24]), "+r"(b[25]), "+r"(b[26]), "+r"(b[27]),
+                 "+r"(b[28]), "+r"(b[29]), "+r"(b[30]), "+r"(b[31])
                :
                : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_plain() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Two fp32 FMAs per instruction (sm_100): d.xy = a.xy * b.xy + d.xy on packed register pairs.
+__device__ __forceinline__ void fma2(uint64_t& d, uint32_t a_lo, uint32_t a_hi, uint64_t b) {
+  uint64_t a;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "r"(a_lo), "r"(a_hi));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+template <int N> __device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
@@ -253,7 +312,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const int kblocks = g.k / BK;
   const int num_m_tiles = g.tiles != nullptr ? __ldg(reinterpret_cast<const int*>(g.tiles)) : g.num_m_tiles_static;
   const int total_tiles = num_m_tiles * g.num_n_tiles;
-  const unsigned long long limit = g.timeout_ns;
+  const unsigned long long limit = g.timeout_cycles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -283,8 +342,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
+  if (warp >= EPI_WARPS) {
+    // third warpgroup: give registers away, then run the producer / MMA roles
+    reg_dec<REGS_OTHER>();
+  // The producer and MMA warps run their loops with all 32 lanes converged and elect one lane
+  // only around the TMA / tcgen05 instructions: addresses, descriptors and barrier operands then
+  // live in uniform registers.  With a single lane running the whole loop the same instructions
+  // were issued from per-thread registers and each tcgen05.mma held the warp's scheduler
+  // partition for ~120 cycles, starving the two promotion warps that share it.
   if (warp == PRODUCER_WARP) {
-    if (lane == 0) {
+    {
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -298,28 +365,31 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-          mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-          tma_load_2d(a_dst, &tmap_a, kb * BK, ti.row0, full_bar(s));
-          if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
-            // gate rows [n0, n0+128) and up rows [n_half + n0, ...+128) of expert e
-            tma_load_2d(b_dst, &tmap_b, kb * BK, ti.e * g.n + ti.n0, full_bar(s));
-            tma_load_2d(b_dst + 128 * BK, &tmap_b, kb * BK, ti.e * g.n + g.n_half + ti.n0, full_bar(s));
-          } else {
+          if (elect_one()) {
+            mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+            tma_load_2d(a_dst, &tmap_a, kb * BK, ti.row0, full_bar(s));
+            if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
+              // gate rows [n0, n0+128) and up rows [n_half + n0, ...+128) of expert e
+              tma_load_2d(b_dst, &tmap_b, kb * BK, ti.e * g.n + ti.n0, full_bar(s));
+              tma_load_2d(b_dst + 128 * BK, &tmap_b, kb * BK, ti.e * g.n + g.n_half + ti.n0, full_bar(s));
+            } else {
 #pragma unroll
-            for (int h = 0; h < BN / 128; ++h)
-              tma_load_2d(b_dst + h * 128 * BK, &tmap_b, kb * BK, ti.e * g.n + ti.n0 + h * 128, full_bar(s));
+              for (int h = 0; h < BN / 128; ++h)
+                tma_load_2d(b_dst + h * 128 * BK, &tmap_b, kb * BK, ti.e * g.n + ti.n0 + h * 128, full_bar(s));
+            }
           }
+          __syncwarp();
         }
       }
       if (!ok) {
         // drain: give the loads of the last STAGES iterations a bounded chance to land
         const uint32_t first = it > (uint32_t)C::STAGES ? it - C::STAGES : 0u;
         for (uint32_t i = first; i < it; ++i)
-          mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1u, abort_flag + 1, 20000000ull);
+          mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1u, abort_flag + 1, 40000000ull);
       }
     }
   } else if (warp == MMA_WARP) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = make_idesc(BN);
       uint32_t it = 0;
       bool ok = true;
@@ -337,22 +407,28 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const uint64_t a_desc = make_smem_desc(a_addr);
           const uint64_t b_desc = make_smem_desc(a_addr + A_STAGE_BYTES);
           const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < BK / 32; ++kk) {
-            // +32 bytes along K inside the 128 B swizzle row == +2 in the (addr >> 4) field
-            tc_mma_f8(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < BK / 32; ++kk) {
+              // +32 bytes along K inside the 128 B swizzle row == +2 in the (addr >> 4) field
+              tc_mma_f8(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, kk > 0 ? 1u : 0u);
+            }
+            tc_commit(empty_bar(s));   // smem stage reusable once these MMAs retire
+            tc_commit(tfull_bar(b));   // accumulator ready for the promotion warps
           }
-          tc_commit(empty_bar(s));   // smem stage reusable once these MMAs retire
-          tc_commit(tfull_bar(b));   // accumulator ready for the promotion warps
+          __syncwarp();
         }
       }
       if (!ok) {
-        tc_commit(drain_bar);
-        mbar_wait(drain_bar, 0, abort_flag + 1, 20000000ull);
+        if (elect_one()) tc_commit(drain_bar);
+        __syncwarp();
+        mbar_wait(drain_bar, 0, abort_flag + 1, 40000000ull);
       }
     }
+  }
   } else {
     // ---- promotion + epilogue warps ------------------------------------------
+    reg_inc<REGS_PROMOTION>();
     const int wg = warp >> 2;                 // 0 or 1
     const int quad = warp & 3;                // TMEM lane quadrant of this warp
     const int r = quad * 32 + lane;           // row inside the tile
@@ -393,71 +469,116 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         bs_ptr[0] = be + (long long)nb0 * kblocks;
         bs_ptr[1] = be + (long long)nb1 * kblocks;
       }
-      float acc[2 * SEG];
+      uint64_t acc2[SEG];                 // 2 * SEG fp32 accumulators, packed in pairs
 #pragma unroll
-      for (int j = 0; j < 2 * SEG; ++j) acc[j] = 0.f;
-
-      float a_sc = __ldg(as_ptr);
-      float b_sc0 = __ldg(bs_ptr[0]);
-      float b_sc1 = __ldg(bs_ptr[1]);
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        const int b = it % C::TMEM_BUFS;
-        // prefetch the next block's scales while waiting for the accumulator
-        float a_nx = 0.f, b_nx0 = 0.f, b_nx1 = 0.f;
-        if (kb + 1 < kblocks) {
-          a_nx = __ldg(as_ptr + (long long)(kb + 1) * g.a_s_ks);
-          b_nx0 = __ldg(bs_ptr[0] + kb + 1);
-          b_nx1 = __ldg(bs_ptr[1] + kb + 1);
+      for (int j = 0; j < SEG; ++j) acc2[j] = 0ull;
+      // row / weight of the scatter epilogue, fetched now so that the two dependent loads are
+      // long done when the tile's last K block arrives
+      long long crow = p;
+      float row_w = 1.f;
+      if constexpr (MODE == DLB_EPI_SCATTER_WEIGHT) {
+        if (row_ok) {
+          crow = g.sorted_idx[p];
+          row_w = g.weights[crow];
         }
-        if (!mbar_wait(tfull_bar(b), (it / C::TMEM_BUFS) & 1u, abort_flag, limit)) {
-          ok = false;
+      }
+
+      // scales are fetched two K blocks ahead: under full TMA load an L2 round trip can take
+      // longer than one K block
+      float a_sc = __ldg(as_ptr), b_sc0 = __ldg(bs_ptr[0]), b_sc1 = __ldg(bs_ptr[1]);
+      float a_n1 = 0.f, b0_n1 = 0.f, b1_n1 = 0.f;
+      if (kblocks > 1) {
+        a_n1 = __ldg(as_ptr + g.a_s_ks);
+        b0_n1 = __ldg(bs_ptr[0] + 1);
+        b1_n1 = __ldg(bs_ptr[1] + 1);
+      }
+      // Two 32-column staging buffers.  A K block is drained in NB batches of two loads; the
+      // loads of the next batch (or of the next K block's first batch) are issued as soon as a
+      // staging buffer has been folded into the accumulators, so a load is always in flight.
+      constexpr int CH = 2 * SEG / 32;   // 32-column chunks per thread and K block (2 or 4)
+      constexpr int NB = CH / 2;
+      auto chunk_col = [&](int c) { return (c * 32 < SEG) ? seg_col[0] + c * 32 : seg_col[1] + c * 32 - SEG; };
+      uint32_t s0[32], s1[32];
+      bool pending = false;              // first batch of the current K block already issued
+      for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
+        const int b = it % C::TMEM_BUFS;
+        const uint32_t buf_addr = lane_addr + (uint32_t)(b * BN);
+        float a_n2 = 0.f, b0_n2 = 0.f, b1_n2 = 0.f;
+        if (kb + 2 < kblocks) {
+          a_n2 = __ldg(as_ptr + (long long)(kb + 2) * g.a_s_ks);
+          b0_n2 = __ldg(bs_ptr[0] + kb + 2);
+          b1_n2 = __ldg(bs_ptr[1] + kb + 2);
+        }
+        if (!pending) {
+          if (!mbar_wait(tfull_bar(b), (it / C::TMEM_BUFS) & 1u, abort_flag, limit)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          tmem_ld32(buf_addr + chunk_col(0), s0);
+          tmem_ld32(buf_addr + chunk_col(1), s1);
+        }
+        pending = false;
+        const float sc0f = a_sc * b_sc0, sc1f = a_sc * b_sc1;
+        const uint64_t sc0 = pack2(sc0f, sc0f);
+        const uint64_t sc1 = pack2(sc1f, sc1f);
+        const bool has_next = kb + 1 < kblocks;
+        const int nb_buf = (it + 1) % C::TMEM_BUFS;
+        const uint32_t next_addr = lane_addr + (uint32_t)(nb_buf * BN);
+#pragma unroll
+        for (int q = 0; q < NB; ++q) {
+          tmem_ld_wait(s0, s1);
+          const bool last = (q == NB - 1);
+          if (last) {
+            // every column of this accumulator is in registers: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(b));
+          }
+          {
+            const uint64_t sc = ((2 * q) * 32 < SEG) ? sc0 : sc1;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) fma2(acc2[(2 * q) * 16 + j], s0[2 * j], s0[2 * j + 1], sc);
+          }
+          if (!last) {
+            tmem_ld32(buf_addr + chunk_col(2 * q + 2), s0);
+          } else if (has_next) {
+            if (!mbar_wait(tfull_bar(nb_buf), ((it + 1) / C::TMEM_BUFS) & 1u, abort_flag, limit)) {
+              ok = false;
+            } else {
+              tc_fence_after();
+              tmem_ld32(next_addr + chunk_col(0), s0);
+            }
+          }
+          {
+            const uint64_t sc = ((2 * q + 1) * 32 < SEG) ? sc0 : sc1;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) fma2(acc2[(2 * q + 1) * 16 + j], s1[2 * j], s1[2 * j + 1], sc);
+          }
+          if (!last) {
+            tmem_ld32(buf_addr + chunk_col(2 * q + 3), s1);
+          } else if (has_next && ok) {
+            tmem_ld32(next_addr + chunk_col(1), s1);
+            pending = true;
+          }
+        }
+        if (!ok) {
+          tmem_ld_wait_plain();
           break;
         }
-        tc_fence_after();
-        const float sc0 = a_sc * b_sc0;
-        const float sc1 = a_sc * b_sc1;
-        const uint32_t buf_addr = lane_addr + (uint32_t)(b * BN);
-        // 16-column chunks, two staging buffers: the load of chunk c+1 is in flight
-        // while chunk c is folded into the accumulators.
-        constexpr int CH = 2 * SEG / 16;
-        uint32_t v0[16], v1[16];
-        tmem_ld16(buf_addr + seg_col[0], v0);
-#pragma unroll
-        for (int c = 0; c < CH; c += 2) {
-          {
-            const int cc = c + 1;
-            const int col = (cc * 16 < SEG) ? seg_col[0] + cc * 16 : seg_col[1] + cc * 16 - SEG;
-            tmem_ld_wait(v0);
-            tmem_ld16(buf_addr + col, v1);
-            const float sc = (c * 16 < SEG) ? sc0 : sc1;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(__uint_as_float(v0[j]), sc, acc[c * 16 + j]);
-          }
-          {
-            const int cc = c + 2;
-            tmem_ld_wait(v1);
-            if (cc < CH) {
-              const int col = (cc * 16 < SEG) ? seg_col[0] + cc * 16 : seg_col[1] + cc * 16 - SEG;
-              tmem_ld16(buf_addr + col, v0);
-            } else {
-              // all columns of this accumulator are in registers: hand it back to the MMA warp
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(tempty_bar(b));
-            }
-            const float sc = ((c + 1) * 16 < SEG) ? sc0 : sc1;
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              acc[(c + 1) * 16 + j] = fmaf(__uint_as_float(v1[j]), sc, acc[(c + 1) * 16 + j]);
-          }
-        }
-        a_sc = a_nx;
-        b_sc0 = b_nx0;
-        b_sc1 = b_nx1;
+        a_sc = a_n1;
+        b_sc0 = b0_n1;
+        b_sc1 = b1_n1;
+        a_n1 = a_n2;
+        b0_n1 = b0_n2;
+        b1_n1 = b1_n2;
       }
       if (!ok) break;
 
       // ---- epilogue ---------------------------------------------------------
+      float acc[2 * SEG];
+#pragma unroll
+      for (int j = 0; j < SEG; ++j) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
       if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
         // reference rounding points: GEMM1 output -> OutT, silu(gate)*up -> OutT, then
         // scale = absmax * (1/448), q = h / scale (dlblas/kernels/moe.py:398-417).
@@ -500,12 +621,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
       } else {
         if (row_ok) {
-          long long crow = p;
           if constexpr (MODE == DLB_EPI_SCATTER_WEIGHT) {
-            crow = g.sorted_idx[p];
-            const float w = g.weights[crow];
 #pragma unroll
-            for (int j = 0; j < 2 * SEG; ++j) acc[j] *= w;
+            for (int j = 0; j < 2 * SEG; ++j) acc[j] *= row_w;
           }
           const int col0 = ti.n0 + seg_col[0];
           OutT* dst = reinterpret_cast<OutT*>(g.c) + crow * g.ldc + col0;
@@ -609,7 +727,7 @@ int check_device() {
   return DLB_OK;
 }
 
-constexpr unsigned long long DEFAULT_TIMEOUT_NS = 2000000000ull;  // 2 s per barrier wait
+constexpr unsigned long long DEFAULT_TIMEOUT_CYCLES = 4000000000ull;  // about 2 s per barrier wait
 
 }  // namespace
 }  // namespace dlb
@@ -653,7 +771,7 @@ extern "C" int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int6
   g.num_m_tiles_static = m_tiles;
   g.num_n_tiles = (int)ceil_div(n, bn);
   g.status = status;
-  g.timeout_ns = DEFAULT_TIMEOUT_NS;
+  g.timeout_cycles = DEFAULT_TIMEOUT_CYCLES;
   const long long total = (long long)m_tiles * g.num_n_tiles;
   const int grid = (int)(total < sms ? total : sms);
   return launch_typed<DLB_EPI_STORE>(bn, c_dtype, ma, mb, g, grid, (cudaStream_t)stream);
@@ -698,7 +816,7 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t row
   g.sorted_idx = reinterpret_cast<const long long*>(sorted_idx);
   g.weights = weights;
   g.status = status;
-  g.timeout_ns = DEFAULT_TIMEOUT_NS;
+  g.timeout_cycles = DEFAULT_TIMEOUT_CYCLES;
   int bn = 256;
   if (epilogue == DLB_EPI_SWIGLU_QUANT) {
     DLB_REQUIRE(n % 256 == 0, DLB_ERR_INVALID, "grouped_gemm: swiglu epilogue needs n %% 256 == 0 (n=%lld)",
