@@ -1,0 +1,69 @@
+"""Expert-parallel layers on 2 GPUs (NCCL): FusedMoENormal and FusedMoELowLatency against the CPU
+oracle of the full layer.  Skipped when fewer than 2 GPUs are visible."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    import torch.distributed as dist
+
+    from dlblas_b200 import _C
+    from dlblas_b200.layers.moe.ep_moe import build_deepep_moe
+    from oracle import moe_oracle as O
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        e, k, h, inter = 16, 4, 512, 256
+        nle = e // world
+        # every rank builds the same weights (seed 0) and its own tokens
+        _, _, w13, w13s, w2, w2s = O.make_layer_inputs(1, h, inter, e, seed=0)
+        t = 96 + 32 * rank
+        g = torch.Generator().manual_seed(10 + rank)
+        x = torch.randn(t, h, generator=g).to(torch.bfloat16)
+        logits = torch.randn(t, e, generator=g)
+        ow, oids = O.softmax_topk(logits, k, True)
+        ref = O.moe_layer(x, ow, oids, w13, w13s, w2, w2s, top_k=k)
+        sl = slice(rank * nle, (rank + 1) * nle)
+        local = [w13[sl].to(dev), w13s[sl].to(dev), w2[sl].to(dev), w2s[sl].to(dev)]
+        for low_latency in (False, True):
+            layer = build_deepep_moe(low_latency, world, dist.group.WORLD, e, h, 128, k, torch.bfloat16)
+            out = layer.forward(x.to(dev), ow.to(dev), oids.to(dev), *local)
+            _C.check_status(dev)
+            err = O.rel_frobenius(out.cpu(), ref)
+            assert out.shape == (t, h) and err < 2e-2, (low_latency, err)
+        ret[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_layers_two_gpus():
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert dict(ret) == {0: "ok", 1: "ok"}
