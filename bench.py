@@ -305,9 +305,9 @@ def run_b200(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        for _ in range(3):
-            step_resident()          # the sampler needs a moment to come up
-        time.sleep(0.3)
+    for _ in range(3):
+        step_resident()              # every rank (the step has collectives); the sampler comes up meanwhile
+    time.sleep(0.3)
     barrier()
     _C.launch_count(reset=True)
     wall0 = time.time()

@@ -156,14 +156,14 @@ class TokenDispatcherNormal:
         # pack: one pass over the tokens, each row copied to its (<= W) destinations
         send_x, send_s = ops.permute_rows(x_q.view(torch.uint8) if x_q.dtype != torch.uint8 else x_q,
                                           x_s, plan.dst_pos, w_sz, n_send)
-        # small per-row metadata: local ids and weights, packed in the same order
-        tok = torch.arange(t, device=dev)[:, None].expand(t, w_sz)
+        # small per-row metadata (local ids, weights), scattered to the same send positions
         sel = plan.dst_pos >= 0
-        order = torch.argsort(plan.dst_pos[sel].to(torch.int64))
-        src_tok = tok[sel][order]
-        dest_rank = torch.arange(w_sz, device=dev)[None, :].expand(t, w_sz)[sel][order]
-        send_ids = localize_ids(topk_idx.to(torch.int64)[src_tok], dest_rank, nle)
-        send_w = topk_weights.to(torch.float32)[src_tok]
+        pos = plan.dst_pos[sel].to(torch.int64)
+        tok_of, rank_of = sel.nonzero(as_tuple=True)
+        send_ids = torch.empty(n_send, k, dtype=torch.int64, device=dev)
+        send_w = torch.empty(n_send, k, dtype=torch.float32, device=dev)
+        send_ids[pos] = localize_ids(topk_idx.to(torch.int64)[tok_of], rank_of, nle)
+        send_w[pos] = topk_weights.to(torch.float32)[tok_of]
         recv_x = torch.empty(n_recv, x_q.shape[1], dtype=torch.uint8, device=dev)
         recv_ids = torch.empty(n_recv, k, dtype=torch.int64, device=dev)
         recv_w = torch.empty(n_recv, k, dtype=torch.float32, device=dev)
