@@ -47,6 +47,8 @@ struct GemmArgs {
   void* c;
   long long ldc;
   float* q_scale;             // SWIGLU_QUANT: [rows, n_half/128]
+  int quant_mode;             // SWIGLU_QUANT: DLB_QUANT_RECIP_MUL or DLB_QUANT_DIV_EPS
+  float quant_eps;
   const int4* tiles;          // nullptr: dense, M tiles derived from m
   int m, n, k;
   int n_half;                 // SWIGLU_QUANT: intermediate size (n / 2)
@@ -532,7 +534,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           break;
         }
         amax = fmaxf(fmaxf(xb[r], xb[BM + r]), fmaxf(xb[2 * BM + r], xb[3 * BM + r]));
-        const float scale = amax * (1.0f / 448.0f);
+        const float scale = g.quant_mode == DLB_QUANT_RECIP_MUL ? amax * (1.0f / 448.0f)
+                                                                : fmaxf(amax, g.quant_eps) / 448.0f;
         if (row_ok) {
           uint8_t* dst = reinterpret_cast<uint8_t*>(g.c) + p * g.ldc + ti.n0 + cg * OUTS;
 #pragma unroll
@@ -709,6 +712,7 @@ extern "C" int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int6
 extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a, const void* b, const float* b_s,
                                     int num_local_experts, int64_t n, int64_t k, const int32_t* tiles, int max_tiles,
                                     int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
+                                    int quant_mode, float quant_eps,
                                     const int64_t* sorted_idx, const float* weights, int32_t* status, void* stream) {
   DLB_REQUIRE(rows_a >= 0 && n > 0 && k > 0 && num_local_experts > 0 && max_tiles >= 0, DLB_ERR_INVALID,
               "grouped_gemm: bad sizes rows=%lld n=%lld k=%lld experts=%d", (long long)rows_a, (long long)n,
@@ -737,6 +741,8 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t row
   g.c = c;
   g.ldc = ldc;
   g.q_scale = q_scale;
+  g.quant_mode = quant_mode;
+  g.quant_eps = quant_eps;
   g.tiles = reinterpret_cast<const int4*>(tiles);
   g.m = (int)rows_a;
   g.n = (int)n;

@@ -300,6 +300,22 @@ __global__ void __launch_bounds__(THREADS) scatter_index_kernel(const IdxT* __re
   }
 }
 
+template <typename IdxT>
+__global__ void __launch_bounds__(THREADS) dest_ranks_kernel(const IdxT* __restrict__ ids, long long tokens, int top_k,
+                                                             int num_local, int world, int* __restrict__ dest) {
+  const long long total = tokens * world;
+  for (long long u = (long long)blockIdx.x * THREADS + threadIdx.x; u < total; u += (long long)gridDim.x * THREADS) {
+    const long long t = u / world;
+    const int r = (int)(u - t * world);
+    bool hit = false;
+    for (int j = 0; j < top_k; ++j) {
+      const long long id = (long long)ids[t * top_k + j];
+      hit = hit || (id >= 0 && id / num_local == r);
+    }
+    dest[u] = hit ? r : world;
+  }
+}
+
 int grid_for(long long total_threads) {
   long long blocks = ceil_div(total_threads, THREADS);
   const long long cap = (long long)sm_count() * 16;
@@ -547,4 +563,23 @@ extern "C" int dlb_ep_scatter(const void* x, int64_t row_bytes, const float* x_s
   count_launch();
   DLB_CHECK_LAUNCH("scatter_index_kernel");
   return dlb_permute_rows(x, row_bytes, x_scale, groups, tokens, dst_pos, top_k, out_x, out_scale, stream);
+}
+
+extern "C" int dlb_ep_dest_ranks(const void* ids, int ids_dtype, int64_t tokens, int top_k, int num_local_experts,
+                                 int world, int32_t* dest, void* stream) {
+  DLB_REQUIRE(tokens >= 0 && top_k > 0 && num_local_experts > 0 && world > 0, DLB_ERR_INVALID, "ep_dest_ranks: bad sizes");
+  DLB_REQUIRE(ids_dtype == DLB_I32 || ids_dtype == DLB_I64, DLB_ERR_INVALID, "ep_dest_ranks: ids must be int32/int64");
+  if (tokens == 0) return DLB_OK;
+  DLB_REQUIRE(ids && dest, DLB_ERR_INVALID, "ep_dest_ranks: null pointer");
+  const int grid = grid_for(tokens * world);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (ids_dtype == DLB_I32)
+    dest_ranks_kernel<int><<<grid, THREADS, 0, st>>>(reinterpret_cast<const int*>(ids), tokens, top_k, num_local_experts,
+                                                    world, dest);
+  else
+    dest_ranks_kernel<long long><<<grid, THREADS, 0, st>>>(reinterpret_cast<const long long*>(ids), tokens, top_k,
+                                                          num_local_experts, world, dest);
+  count_launch();
+  DLB_CHECK_LAUNCH("dest_ranks_kernel");
+  return DLB_OK;
 }

@@ -75,7 +75,7 @@ __device__ __forceinline__ void scatter_chunk(const IdT* ids, long long n, int n
     if (f < end) {
       const int pos = old + rank;
       if (o.sorted_idx) o.sorted_idx[pos] = f;
-      if (o.slot_pos) o.slot_pos[f] = b == 0 ? -(pos + 1) : pos;
+      if (o.slot_pos) o.slot_pos[f] = (b == 0 || b == num_experts + 1) ? -(pos + 1) : pos;
       if (o.rank_in_expert) o.rank_in_expert[f] = (b >= 1 && b <= num_experts) ? pos - base[b] : -1;
     }
   }

@@ -44,9 +44,11 @@ class FusedMoENormal:
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,
                 up_weights: torch.Tensor, up_scale: torch.Tensor, down_weights: torch.Tensor,
                 down_scale: torch.Tensor, expert_list: List[int] = None):
-        hs_quant, hs_scale = per_token_group_quant_fp8(hidden_states, self.block_size)
-        x, recv_topk_ids, recv_topk_weights, recv_tokens_per_expert = self.token_dispatcher.dispatch(
-            (hs_quant, hs_scale), topk_ids, topk_weights, expert_list)
+        # per_token_group_quant_fp8 fused with the packing of the send buffer (one pass over the tokens)
+        x, recv_topk_ids, recv_topk_weights, recv_tokens_per_expert = self.token_dispatcher.dispatch_from_hidden(
+            hidden_states.flatten(0, -2) if hidden_states.dim() > 2 else hidden_states, topk_ids, topk_weights,
+            self.block_size)
+        self.token_dispatcher.hidden_shape = hidden_states.shape
         out_states = fused_moe_v3(x, recv_topk_ids, recv_topk_weights, (up_weights, up_scale),
                                   (down_weights, down_scale), recv_tokens_per_expert)
         return self.token_dispatcher.combine(out_states)

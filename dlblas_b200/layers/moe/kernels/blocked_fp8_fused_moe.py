@@ -54,9 +54,9 @@ def moe_expert_forward(hidden: Optional[torch.Tensor], x_q: Optional[torch.Tenso
         a1, a1_s = ops.permute_rows(x_q, x_s.contiguous(), pos, topk, s_rows)
     h_q = torch.empty(s_rows, inter, dtype=ops.FP8, device=dev)
     h_s = torch.empty(s_rows, inter // 128, dtype=torch.float32, device=dev)
-    if fuse_swiglu and quant_mode == _C.QUANT_RECIP_MUL and n % 256 == 0:
+    if fuse_swiglu and n % 256 == 0:
         ops.grouped_gemm(a1, a1_s, w1, w1_scale, tiles, max_tiles, _C.EPI_SWIGLU_QUANT, h_q, q_scale=h_s,
-                         round_dtype=out_dtype)
+                         round_dtype=out_dtype, quant_mode=quant_mode, quant_eps=1e-10)
     else:
         c1 = torch.empty(s_rows, n, dtype=out_dtype, device=dev)
         ops.grouped_gemm(a1, a1_s, w1, w1_scale, tiles, max_tiles, _C.EPI_STORE, c1)

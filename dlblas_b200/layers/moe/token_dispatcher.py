@@ -55,19 +55,30 @@ class NormalPlan:
 
 def make_normal_plan(topk_ids: torch.Tensor, world_size: int, rank: int, num_local_experts: int,
                      group, expert_alignment: int = 128) -> NormalPlan:
-    """topk_ids: [T, k] global expert ids (any negative id = unrouted slot)."""
+    """topk_ids: [T, k] global expert ids (any negative id = unrouted slot).
+
+    dst_pos[t, r] is the row of token t in the part of the send buffer that goes to rank r (rows of
+    one rank are contiguous and in token order) or negative if rank r owns none of its experts.  On
+    CUDA this is the stable counting sort of the extension applied to the (token, rank) pairs; the
+    torch formulation below it is the same computation for CPU tensors."""
     t, k = topk_ids.shape
     dev = topk_ids.device
     ids = topk_ids.to(torch.int64)
     valid = ids >= 0
-    owner = torch.where(valid, ids // num_local_experts, torch.full_like(ids, world_size))
-    need = torch.zeros(t, world_size + 1, dtype=torch.int32, device=dev)
-    need.scatter_(1, owner, 1)
-    need = need[:, :world_size]                                   # [T, W] 0/1
-    per_rank = need.sum(dim=0, dtype=torch.int64)                 # rows sent to each rank
-    offs = torch.cumsum(per_rank, 0) - per_rank
-    within = torch.cumsum(need, dim=0, dtype=torch.int64) - need  # rank of the token among the rank's rows
-    dst_pos = torch.where(need > 0, offs[None, :] + within, torch.full_like(within, -1)).to(torch.int32)
+    if topk_ids.is_cuda:
+        dest = ops.ep_dest_ranks(topk_ids.contiguous(), num_local_experts, world_size)
+        _, _, _, pos, cnt = ops.sort_by_expert(dest, world_size, want_pos=True, want_counts=True)
+        dst_pos = pos.view(t, world_size)
+        per_rank = cnt.to(torch.int64)
+    else:
+        owner = torch.where(valid, ids // num_local_experts, torch.full_like(ids, world_size))
+        need = torch.zeros(t, world_size + 1, dtype=torch.int32, device=dev)
+        need.scatter_(1, owner, 1)
+        need = need[:, :world_size]                                   # [T, W] 0/1
+        per_rank = need.sum(dim=0, dtype=torch.int64)                 # rows sent to each rank
+        offs = torch.cumsum(per_rank, 0) - per_rank
+        within = torch.cumsum(need, dim=0, dtype=torch.int64) - need  # rank of the token among the rank's rows
+        dst_pos = torch.where(need > 0, offs[None, :] + within, torch.full_like(within, -1)).to(torch.int32)
     per_expert = torch.bincount(ids[valid], minlength=world_size * num_local_experts)[:world_size * num_local_experts]
     mine = torch.cat([per_rank[:, None], per_expert.view(world_size, num_local_experts)], dim=1).contiguous()
     gathered = torch.empty(world_size, world_size, num_local_experts + 1, dtype=torch.int64, device=dev)
@@ -145,39 +156,61 @@ class TokenDispatcherNormal:
     # ---- async flavoured API (same stream; events mark completion) ----------------------------
     def dispatch_normal_async(self, x, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
                               num_experts: Optional[int] = None, previous_event=None, async_finish=True):
+        """x: (e4m3 rows, fp32 scales) or unquantised rows.  Returns (recv_x, recv_topk_idx (local ids, -1 for
+        other ranks' experts), recv_topk_weights, recv_tokens_per_expert (list, aligned), handle, event)."""
         if previous_event is not None:
             previous_event.current_stream_wait()
         x_q, x_s = x if isinstance(x, tuple) else (x, None)
-        w_sz, nle = self.world_size, self.num_local_experts
-        plan = make_normal_plan(topk_idx, w_sz, self.rank, nle, self.group, self.expert_alignment)
-        t, k = topk_idx.shape
-        dev = x_q.device
-        n_send, n_recv = plan.num_send, plan.num_recv
+        w_sz = self.world_size
+        plan = make_normal_plan(topk_idx, w_sz, self.rank, self.num_local_experts, self.group, self.expert_alignment)
         # pack: one pass over the tokens, each row copied to its (<= W) destinations
-        send_x, send_s = ops.permute_rows(x_q.view(torch.uint8) if x_q.dtype != torch.uint8 else x_q,
-                                          x_s, plan.dst_pos, w_sz, n_send)
-        # small per-row metadata (local ids, weights), scattered to the same send positions
-        sel = plan.dst_pos >= 0
-        pos = plan.dst_pos[sel].to(torch.int64)
-        tok_of, rank_of = sel.nonzero(as_tuple=True)
-        send_ids = torch.empty(n_send, k, dtype=torch.int64, device=dev)
-        send_w = torch.empty(n_send, k, dtype=torch.float32, device=dev)
-        send_ids[pos] = localize_ids(topk_idx.to(torch.int64)[tok_of], rank_of, nle)
-        send_w[pos] = topk_weights.to(torch.float32)[tok_of]
-        recv_x = torch.empty(n_recv, x_q.shape[1], dtype=torch.uint8, device=dev)
-        recv_ids = torch.empty(n_recv, k, dtype=torch.int64, device=dev)
-        recv_w = torch.empty(n_recv, k, dtype=torch.float32, device=dev)
+        send_x, send_s = ops.permute_rows(x_q.view(torch.uint8) if x_q.element_size() == 1 else x_q, x_s, plan.dst_pos,
+                                          w_sz, plan.num_send)
+        return self._exchange(plan, send_x, send_s, x_q.dtype, topk_idx, topk_weights)
+
+    def dispatch_from_hidden(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+                             block_size: int = 128):
+        """Quantise (per_token_group_quant_fp8 arithmetic) straight into the send buffer: one kernel reads each
+        token once and writes its FP8 row and scales to every destination rank's part of the buffer."""
+        self.hidden_shape = hidden_states.shape
+        topk_idx = topk_idx.to(torch.int64)
+        plan = make_normal_plan(topk_idx, self.world_size, self.rank, self.num_local_experts, self.group,
+                                self.expert_alignment)
+        send_x, send_s = ops.quant_fp8(hidden_states, block_size, _C.QUANT_DIV_EPS, 1e-10, False, plan.dst_pos,
+                                       self.world_size, plan.num_send)
+        recv_x, recv_idx, recv_w, per_expert, handle, _ = self._exchange(plan, send_x.view(torch.uint8), send_s,
+                                                                         ops.FP8, topk_idx, topk_weights)
+        self.handle, self.topk_idx, self.topk_weights = handle, recv_idx, recv_w
+        return recv_x, recv_idx, recv_w, per_expert
+
+    def _exchange(self, plan, send_x, send_s, x_dtype, topk_idx, topk_weights):
+        w_sz, nle = self.world_size, self.num_local_experts
+        t, k = topk_idx.shape
+        dev = send_x.device
+        n_send, n_recv = plan.num_send, plan.num_recv
+        # per-row metadata travels as one [*, 2 kp] int32 row: global ids and the weights' bit patterns
+        kp = (k + 1) // 2 * 2
+        meta = torch.zeros(t, 2 * kp, dtype=torch.int32, device=dev)
+        meta[:, :k] = topk_idx
+        meta[:, kp:kp + k] = topk_weights.to(torch.float32).view(torch.int32)
+        send_meta, _ = ops.permute_rows(meta.view(torch.uint8), None, plan.dst_pos, w_sz, n_send)
+        recv_x = torch.empty(n_recv, send_x.shape[1], dtype=send_x.dtype, device=dev)
+        recv_meta = torch.empty(n_recv, 8 * kp, dtype=torch.uint8, device=dev)
         _a2a(recv_x, send_x, plan.recv_splits, plan.send_splits, self.group, w_sz)
         recv_s = None
-        if x_s is not None:
-            recv_s = torch.empty(n_recv, x_s.shape[1], dtype=torch.float32, device=dev)
+        if send_s is not None:
+            recv_s = torch.empty(n_recv, send_s.shape[1], dtype=torch.float32, device=dev)
             _a2a(recv_s, send_s, plan.recv_splits, plan.send_splits, self.group, w_sz)
-        _a2a(recv_ids, send_ids.contiguous(), plan.recv_splits, plan.send_splits, self.group, w_sz)
-        _a2a(recv_w, send_w.contiguous(), plan.recv_splits, plan.send_splits, self.group, w_sz)
-        recv_x = recv_x.view(x_q.dtype)
-        out_x = (recv_x, recv_s) if x_s is not None else recv_x
-        handle = (plan,)
-        return out_x, recv_ids, recv_w, plan.recv_tokens_per_expert, handle, _record_event()
+        _a2a(recv_meta, send_meta, plan.recv_splits, plan.send_splits, self.group, w_sz)
+        rm = recv_meta.view(torch.int32)
+        lo = self.rank * nle
+        gid = rm[:, :k].to(torch.int64)
+        recv_ids = torch.where((gid >= lo) & (gid < lo + nle), gid - lo, torch.full_like(gid, -1))
+        recv_w = rm[:, kp:kp + k].view(torch.float32).contiguous()
+        if recv_x.dtype != x_dtype:
+            recv_x = recv_x.view(x_dtype)
+        out_x = (recv_x, recv_s) if send_s is not None else recv_x
+        return out_x, recv_ids, recv_w, plan.recv_tokens_per_expert, (plan,), _record_event()
 
     def combine_normal_async(self, x: torch.Tensor, handle: Tuple, previous_event=None, async_finish=True):
         if previous_event is not None:

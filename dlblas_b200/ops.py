@@ -155,7 +155,8 @@ def fp8_gemm(a: torch.Tensor, b: torch.Tensor, a_s: torch.Tensor, b_s: torch.Ten
 def grouped_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch.Tensor, tiles: torch.Tensor,
                  max_tiles: int, epilogue: int, c: torch.Tensor, q_scale: Optional[torch.Tensor] = None,
                  sorted_idx: Optional[torch.Tensor] = None, weights: Optional[torch.Tensor] = None,
-                 round_dtype: Optional[torch.dtype] = None):
+                 round_dtype: Optional[torch.dtype] = None, quant_mode: int = _C.QUANT_RECIP_MUL,
+                 quant_eps: float = 1e-10):
     """a [rows, k] e4m3 in expert-contiguous order, b [E, n, k]; see dlb_moe_grouped_gemm."""
     require_cuda(a, b)
     assert a.is_contiguous() and a_s.is_contiguous() and b.is_contiguous() and b_s.is_contiguous()
@@ -167,7 +168,8 @@ def grouped_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch
     else:
         cdt = dtype_code(c.dtype)
     check(lib().dlb_moe_grouped_gemm(ptr(a), ptr(a_s), rows, ptr(b), ptr(b_s), e, n, k, ptr(tiles), max_tiles, epilogue,
-                                     ptr(c), cdt, c.stride(0), ptr(q_scale), ptr(sorted_idx), ptr(weights),
+                                     ptr(c), cdt, c.stride(0), ptr(q_scale), quant_mode, quant_eps, ptr(sorted_idx),
+                                     ptr(weights),
                                      ptr(_C.status_word(a.device)), stream(a.device)))
     return c
 
@@ -259,3 +261,14 @@ def topk_gating(logits: torch.Tensor, k: int, capacity: int):
     check(lib().dlb_topk_gating(ptr(logits), dtype_code(logits.dtype), t, e, k, capacity, ptr(l_aux), ptr(ec_idx), ptr(w),
                                 ptr(sel), ptr(ws), ws_bytes, stream(dev)))
     return l_aux, ec_idx, w, sel
+
+
+def ep_dest_ranks(topk_ids: torch.Tensor, num_local_experts: int, world_size: int) -> torch.Tensor:
+    """int32 [T * W]: entry t*W + r is r if token t routes to an expert of rank r, else W."""
+    require_cuda(topk_ids)
+    assert topk_ids.is_contiguous() and topk_ids.dtype in (torch.int32, torch.int64)
+    t, k = topk_ids.shape
+    out = torch.empty(t * world_size, dtype=torch.int32, device=topk_ids.device)
+    check(lib().dlb_ep_dest_ranks(ptr(topk_ids), dtype_code(topk_ids.dtype), t, k, num_local_experts, world_size, ptr(out),
+                                  stream(topk_ids.device)))
+    return out

@@ -67,8 +67,9 @@ DLB_API int64_t dlb_launch_count(int reset);
  * sorted_idx[p] = flat slot index at sorted position p (stable: `-1` entries first,
  * ascending flat index inside an expert).  exp_start/exp_end: int64 [num_experts],
  * start = end = 0 for an expert without tokens.  Optional outputs (may be NULL):
- * slot_pos[f] = sorted position p of flat slot f (int32); for a slot with id < 0 it is stored as
- * -(p + 1) so that the permutation kernels, which skip negative destinations, move no data for it.
+ * slot_pos[f] = sorted position p of flat slot f (int32); for a slot whose id is not an expert
+ * (id < 0, or id >= num_experts) it is stored as -(p + 1) so that the permutation kernels, which skip
+ * negative destinations, move no data for it.
  * rank_in_expert[f] = position of slot f inside its expert's segment (int32, -1 for id < 0),
  * counts[e] (int32). */
 DLB_API size_t dlb_sort_by_expert_workspace_size(int64_t num_slots, int num_experts);
@@ -154,10 +155,12 @@ DLB_API int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int64_t
  * dlblas/layers/moe/ep_moe.py:180-197).  a: [rows_a, k] e4m3 in expert-contiguous order,
  * a_s: [rows_a, k/128]; b: [experts, n, k] e4m3; b_s: [experts, n/128, k/128]; tiles from
  * dlb_moe_build_tiles*.  Epilogues: see DLB_EPI_*.  For DLB_EPI_SWIGLU_QUANT n is the width of
- * b (2 * intermediate, gate rows first), c receives e4m3 [rows_a, n/2] and q_scale fp32 [rows_a, n/256]. */
+ * b (2 * intermediate, gate rows first), c receives e4m3 [rows_a, n/2] and q_scale fp32 [rows_a, n/256];
+ * quant_mode / quant_eps choose the scale arithmetic of that re-quantisation (DLB_QUANT_*). */
 DLB_API int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a, const void* b, const float* b_s,
                          int num_local_experts, int64_t n, int64_t k, const int32_t* tiles, int max_tiles,
                          int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
+                         int quant_mode, float quant_eps,
                          const int64_t* sorted_idx, const float* weights, int32_t* status, void* stream);
 
 /* ---- combine -----------------------------------------------------------------
@@ -180,6 +183,13 @@ DLB_API int dlb_ep_scatter(const void* x, int64_t row_bytes, const float* x_scal
                    int32_t* expert_start_loc, void* out_x, float* out_scale, int32_t* m_indices,
                    int64_t m_indices_len, void* output_index, void* workspace, size_t workspace_bytes,
                    void* stream);
+
+/* Destination ranks of an expert-parallel dispatch (the layout step of DeepEP's
+ * Buffer.get_dispatch_layout, dlblas/layers/moe/token_dispatcher.py:330): dest[t*world + r] = r if any
+ * of token t's ids belongs to rank r (ids / num_local_experts == r), else world.  Sorting this array
+ * with dlb_sort_by_expert(num_experts = world) yields every (token, rank) pair's row in the send buffer. */
+DLB_API int dlb_ep_dest_ranks(const void* ids, int ids_dtype, int64_t tokens, int top_k, int num_local_experts,
+                      int world, int32_t* dest, void* stream);
 
 /* ---- routing -------------------------------------------------------------------
  * topk(softmax(logits, fp32), k) with lowest-index tie-break, optional w / sum(w): the routing the
