@@ -159,24 +159,19 @@ def cpu_sample(sample_tokens: int, w_cpu, x, logits, bias):
     return time.perf_counter() - t0, out
 
 
-def cpu_weights(dev_weights=None, seed=0):
-    """fp8 weights on the host: copied back from the device arm's tensors when given, otherwise
-    generated on the host for the hit experts only is not possible up front, so all are generated
-    in chunks (bf16-free, ~11 GB of e4m3)."""
-    if dev_weights is not None:
-        return [w.cpu() for w in dev_weights]
-    g = torch.Generator().manual_seed(seed)
+def cpu_weights(seed=0, distinct=8):
+    """e4m3 weights of all 256 routed experts + the shared expert on the host.  Generating 11 GB of
+    random weights on the CPU would take minutes, so `distinct` experts are drawn and repeated
+    (expert e uses draw e % distinct); the cost of the CPU path does not depend on the values."""
     from oracle import moe_oracle as O
-    w13 = torch.empty(E, 2 * INTER, H, dtype=FP8)
-    w13s = torch.empty(E, 2 * INTER // 128, H // 128)
-    w2 = torch.empty(E, H, INTER, dtype=FP8)
-    w2s = torch.empty(E, H // 128, INTER // 128)
-    for e in range(E):
-        w13[e:e + 1], w13s[e:e + 1] = O.quantize_weight_blocks(torch.randn(1, 2 * INTER, H, generator=g) * 0.02)
-        w2[e:e + 1], w2s[e:e + 1] = O.quantize_weight_blocks(torch.randn(1, H, INTER, generator=g) * 0.02)
+    g = torch.Generator().manual_seed(seed)
+    w13, w13s = O.quantize_weight_blocks(torch.randn(distinct, 2 * INTER, H, generator=g) * 0.02)
+    w2, w2s = O.quantize_weight_blocks(torch.randn(distinct, H, INTER, generator=g) * 0.02)
     sw13, sw13s = O.quantize_weight_blocks(torch.randn(1, 2 * INTER, H, generator=g) * 0.02)
     sw2, sw2s = O.quantize_weight_blocks(torch.randn(1, H, INTER, generator=g) * 0.02)
-    return [w13, w13s, w2, w2s, sw13[0], sw13s[0], sw2[0], sw2s[0]]
+    idx = torch.arange(E) % distinct
+    return [w13.view(torch.uint8)[idx].view(FP8), w13s[idx], w2.view(torch.uint8)[idx].view(FP8), w2s[idx],
+            sw13[0], sw13s[0], sw2[0], sw2s[0]]
 
 
 def run_reference(args):
@@ -185,9 +180,12 @@ def run_reference(args):
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    sample = args.cpu_tokens
-    x, logits, bias = make_tokens(sample, 100)
-    w_cpu = cpu_weights(None, 0)
+    x, logits, bias = make_tokens(max(args.cpu_tokens, 8), 100)
+    w_cpu = cpu_weights(0)
+    # size the per-step sample so that warm-up + timed steps stay near two minutes of CPU work
+    t8, _ = cpu_sample(8, w_cpu, x, logits, bias)
+    budget = 120.0 / max(args.warmup + args.steps, 1)
+    sample = max(1, min(args.cpu_tokens, int(budget / (t8 / 8.0))))
     times = []
     for i in range(args.warmup + args.steps):
         dt, _ = cpu_sample(sample, w_cpu, x, logits, bias)
