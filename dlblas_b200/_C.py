@@ -45,11 +45,15 @@ SIGNATURES = {
     "dlb_moe_grouped_gemm": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_vp,
                                      c_int, c_i64, c_vp, c_int, c_f, c_vp, c_vp, c_vp, c_vp]),
     "dlb_ep_dest_ranks": (c_int, [c_vp, c_int, c_i64, c_int, c_int, c_int, c_vp, c_vp]),
-    "dlb_moe_sum_topk": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_vp, c_int, c_i64, c_i64, c_vp, c_vp]),
+    "dlb_moe_sum_topk": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_vp, c_int, c_i64, c_i64, c_int, c_vp, c_vp]),
     "dlb_ep_gather": (c_int, [c_vp, c_int, c_i64, c_vp, c_vp, c_int, c_vp, c_i64, c_int, c_vp, c_vp]),
     "dlb_ep_scatter_workspace_size": (c_sz, [c_i64, c_int, c_int]),
     "dlb_ep_scatter": (c_int, [c_vp, c_i64, c_vp, c_i64, c_vp, c_int, c_i64, c_int, c_vp, c_int, c_vp, c_vp, c_vp,
                                c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
+    "dlb_p2p_quant_push": (c_int, [c_vp, c_int, c_i64, c_i64, c_i64, c_int, c_f, c_vp, c_int, c_int, c_i64, c_vp, c_vp,
+                                   c_vp, c_vp, c_int, c_vp, c_vp, c_vp]),
+    "dlb_p2p_unpack_meta": (c_int, [c_vp, c_int, c_int, c_vp, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
+    "dlb_p2p_push_rows": (c_int, [c_vp, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
     "dlb_route_softmax_topk": (c_int, [c_vp, c_int, c_i64, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp]),
     "dlb_route_grouped_topk": (c_int, [c_vp, c_int, c_vp, c_i64, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp]),
     "dlb_topk_gating_workspace_size": (c_sz, [c_i64, c_int, c_int]),

@@ -1,0 +1,230 @@
+// Expert-parallel dispatch / combine by direct stores into the peers' memory (NVLink / NVSwitch).
+//
+// Every rank owns a receive buffer of W regions (one per source rank) of `region_rows` rows.
+// The dispatch kernel quantises a token once and stores its FP8 row, scales and routing
+// metadata straight into the region "my rank" of every destination rank that owns one of its
+// experts: the all-to-all is fused with the quantiser and with the permutation, no staging
+// buffer, no host-side split sizes.  The combine kernel pushes result rows back the same way.
+// Cross-rank ordering (a barrier after each push phase) is done by the caller on the stream.
+// Only plain 16-byte global stores through peer pointers are used.
+#include "common.cuh"
+
+namespace dlb {
+namespace {
+
+constexpr int THREADS = 256;
+constexpr int MAX_WORLD = 16;
+
+struct PeerPtrs {
+  void* p[MAX_WORLD];
+};
+
+__device__ __forceinline__ void load8_bf16(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load8_f16(const __half* p, float (&v)[8]) {
+  const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+  const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+// One thread per 8 elements of a token row (16 lanes per 128-wide group), as in the local
+// quantiser; `within[t * world + r]` is the row of token t inside my region on rank r (< 0:
+// rank r gets nothing from this token).
+template <bool IS_BF16>
+__global__ void __launch_bounds__(THREADS) quant_push_kernel(const void* __restrict__ x, long long tokens, long long k,
+                                                             long long ldx, int mode, float eps,
+                                                             const int* __restrict__ within, int world, int my_rank,
+                                                             long long region_rows, PeerPtrs peer_q, PeerPtrs peer_s,
+                                                             PeerPtrs peer_meta, const int* __restrict__ meta,
+                                                             int meta_ints, PeerPtrs peer_counts,
+                                                             const int* __restrict__ counts) {
+  const long long vec_per_row = k / 8;
+  const long long total = tokens * vec_per_row;
+  const long long groups = k / 128;
+  if (blockIdx.x == 0 && threadIdx.x < world)
+    reinterpret_cast<int*>(peer_counts.p[threadIdx.x])[my_rank] = counts[threadIdx.x];
+  for (long long u0 = (long long)blockIdx.x * THREADS; u0 < total; u0 += (long long)gridDim.x * THREADS) {
+    const long long u = u0 + threadIdx.x;
+    const bool active = u < total;
+    const long long row = active ? u / vec_per_row : 0;
+    const long long c = active ? (u - row * vec_per_row) * 8 : 0;
+    float v[8];
+    if (active) {
+      if (IS_BF16) load8_bf16(reinterpret_cast<const __nv_bfloat16*>(x) + row * ldx + c, v);
+      else load8_f16(reinterpret_cast<const __half*>(x) + row * ldx + c, v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = mode == DLB_QUANT_RECIP_MUL ? amax * (1.0f / 448.0f) : fmaxf(amax, eps) / 448.0f;
+    if (!active) continue;
+    uint2 packed;
+    packed.x = (uint32_t)f32x2_to_e4m3x2(v[0] / scale, v[1] / scale) |
+               ((uint32_t)f32x2_to_e4m3x2(v[2] / scale, v[3] / scale) << 16);
+    packed.y = (uint32_t)f32x2_to_e4m3x2(v[4] / scale, v[5] / scale) |
+               ((uint32_t)f32x2_to_e4m3x2(v[6] / scale, v[7] / scale) << 16);
+    const bool first = ((c / 8) & 15) == 0;
+    for (int r = 0; r < world; ++r) {
+      const int j = __ldg(within + row * world + r);
+      if (j < 0) continue;
+      const long long drow = (long long)my_rank * region_rows + j;
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(peer_q.p[r]) + drow * k + c) = packed;
+      if (first) reinterpret_cast<float*>(peer_s.p[r])[drow * groups + c / 128] = scale;
+      if (c == 0) {
+        int* dm = reinterpret_cast<int*>(peer_meta.p[r]) + drow * meta_ints;
+        for (int i = 0; i < meta_ints; ++i) dm[i] = __ldg(meta + row * meta_ints + i);
+      }
+    }
+  }
+}
+
+// Receiver side: turns the metadata rows into local expert ids (-1: not a local expert or an
+// unused row of the region) and weights.
+__global__ void __launch_bounds__(THREADS) unpack_meta_kernel(const int* __restrict__ meta, int meta_ints, int top_k,
+                                                              int kp, const int* __restrict__ counts, int world,
+                                                              long long region_rows, int expert_lo, int num_local,
+                                                              long long* __restrict__ ids, float* __restrict__ weights) {
+  const long long total = (long long)world * region_rows * top_k;
+  for (long long u = (long long)blockIdx.x * THREADS + threadIdx.x; u < total; u += (long long)gridDim.x * THREADS) {
+    const long long row = u / top_k;
+    const int j = (int)(u - row * top_k);
+    const int src = (int)(row / region_rows);
+    const bool used = (row - (long long)src * region_rows) < counts[src];
+    long long id = -1;
+    float w = 0.f;
+    if (used) {
+      const int g = meta[row * meta_ints + j];
+      if (g >= expert_lo && g < expert_lo + num_local) id = g - expert_lo;
+      w = __int_as_float(meta[row * meta_ints + kp + j]);
+    }
+    ids[u] = id;
+    weights[u] = w;
+  }
+}
+
+// Pushes the used rows of each region back to the rank they came from: row j of region s goes to
+// rank s, region "my rank", row j.
+__global__ void __launch_bounds__(THREADS) push_rows_kernel(const uint4* __restrict__ src, long long vec_per_row,
+                                                            const int* __restrict__ counts, int world, int my_rank,
+                                                            long long region_rows, PeerPtrs peer_dst) {
+  const long long total = (long long)world * region_rows * vec_per_row;
+  for (long long u = (long long)blockIdx.x * THREADS + threadIdx.x; u < total; u += (long long)gridDim.x * THREADS) {
+    const long long row = u / vec_per_row;
+    const long long c = u - row * vec_per_row;
+    const int s = (int)(row / region_rows);
+    const long long j = row - (long long)s * region_rows;
+    if (j >= counts[s]) continue;
+    reinterpret_cast<uint4*>(peer_dst.p[s])[((long long)my_rank * region_rows + j) * vec_per_row + c] = __ldg(src + u);
+  }
+}
+
+int grid_for(long long total_threads) {
+  long long blocks = ceil_div(total_threads, THREADS);
+  const long long cap = (long long)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+int fill_peers(PeerPtrs& dst, const void* const* src, int world, const char* what) {
+  for (int r = 0; r < world; ++r) {
+    DLB_REQUIRE(src != nullptr && src[r] != nullptr, DLB_ERR_INVALID, "%s: null peer pointer for rank %d", what, r);
+    DLB_REQUIRE((uintptr_t)src[r] % 16 == 0, DLB_ERR_INVALID, "%s: peer pointer of rank %d is not 16-byte aligned", what, r);
+    dst.p[r] = const_cast<void*>(src[r]);
+  }
+  return DLB_OK;
+}
+
+}  // namespace
+}  // namespace dlb
+
+using namespace dlb;
+
+extern "C" int dlb_p2p_quant_push(const void* x, int x_dtype, int64_t tokens, int64_t k, int64_t ldx, int mode, float eps,
+                                  const int32_t* within, int world, int my_rank, int64_t region_rows,
+                                  const void* const* peer_q, const void* const* peer_scales,
+                                  const void* const* peer_meta, const int32_t* meta, int meta_ints,
+                                  const void* const* peer_counts, const int32_t* counts, void* stream) {
+  DLB_REQUIRE(tokens >= 0 && k > 0 && k % 128 == 0, DLB_ERR_INVALID, "p2p_quant_push: k=%lld must be a multiple of 128",
+              (long long)k);
+  DLB_REQUIRE(world > 0 && world <= MAX_WORLD && my_rank >= 0 && my_rank < world, DLB_ERR_INVALID,
+              "p2p_quant_push: world=%d (max %d), rank=%d", world, MAX_WORLD, my_rank);
+  DLB_REQUIRE(tokens <= region_rows, DLB_ERR_INVALID, "p2p_quant_push: %lld tokens exceed the region of %lld rows",
+              (long long)tokens, (long long)region_rows);
+  DLB_REQUIRE(x_dtype == DLB_BF16 || x_dtype == DLB_F16, DLB_ERR_INVALID, "p2p_quant_push: x must be bf16 or fp16");
+  DLB_REQUIRE(mode == DLB_QUANT_RECIP_MUL || mode == DLB_QUANT_DIV_EPS, DLB_ERR_INVALID, "p2p_quant_push: bad mode");
+  DLB_REQUIRE(meta_ints > 0 && meta_ints % 4 == 0, DLB_ERR_INVALID, "p2p_quant_push: meta_ints must be a multiple of 4");
+  DLB_REQUIRE(within && meta && counts && (tokens == 0 || x), DLB_ERR_INVALID, "p2p_quant_push: null pointer");
+  DLB_REQUIRE(tokens == 0 || ((uintptr_t)x % 16 == 0 && (ldx * 2) % 16 == 0), DLB_ERR_INVALID,
+              "p2p_quant_push: x rows must be 16-byte aligned");
+  PeerPtrs pq, ps, pm, pc;
+  int rc;
+  if ((rc = fill_peers(pq, peer_q, world, "p2p_quant_push(q)")) != DLB_OK) return rc;
+  if ((rc = fill_peers(ps, peer_scales, world, "p2p_quant_push(scales)")) != DLB_OK) return rc;
+  if ((rc = fill_peers(pm, peer_meta, world, "p2p_quant_push(meta)")) != DLB_OK) return rc;
+  if ((rc = fill_peers(pc, peer_counts, world, "p2p_quant_push(counts)")) != DLB_OK) return rc;
+  const int grid = grid_for(tokens * (k / 8));
+  cudaStream_t st = (cudaStream_t)stream;
+  if (x_dtype == DLB_BF16)
+    quant_push_kernel<true><<<grid, THREADS, 0, st>>>(x, tokens, k, ldx, mode, eps, within, world, my_rank, region_rows, pq,
+                                                     ps, pm, meta, meta_ints, pc, counts);
+  else
+    quant_push_kernel<false><<<grid, THREADS, 0, st>>>(x, tokens, k, ldx, mode, eps, within, world, my_rank, region_rows,
+                                                      pq, ps, pm, meta, meta_ints, pc, counts);
+  count_launch();
+  DLB_CHECK_LAUNCH("quant_push_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_p2p_unpack_meta(const int32_t* meta, int meta_ints, int top_k, const int32_t* counts, int world,
+                                   int64_t region_rows, int expert_lo, int num_local_experts, int64_t* ids,
+                                   float* weights, void* stream) {
+  DLB_REQUIRE(meta && counts && ids && weights, DLB_ERR_INVALID, "p2p_unpack_meta: null pointer");
+  DLB_REQUIRE(world > 0 && world <= MAX_WORLD && region_rows > 0 && top_k > 0, DLB_ERR_INVALID,
+              "p2p_unpack_meta: bad sizes");
+  const int kp = meta_ints / 2;
+  DLB_REQUIRE(meta_ints % 4 == 0 && kp >= top_k, DLB_ERR_INVALID, "p2p_unpack_meta: meta_ints=%d too small for top_k=%d",
+              meta_ints, top_k);
+  unpack_meta_kernel<<<grid_for((long long)world * region_rows * top_k), THREADS, 0, (cudaStream_t)stream>>>(
+      meta, meta_ints, top_k, kp, counts, world, region_rows, expert_lo, num_local_experts,
+      reinterpret_cast<long long*>(ids), weights);
+  count_launch();
+  DLB_CHECK_LAUNCH("unpack_meta_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32_t* counts, int world, int my_rank,
+                                 int64_t region_rows, const void* const* peer_dst, void* stream) {
+  DLB_REQUIRE(src && counts, DLB_ERR_INVALID, "p2p_push_rows: null pointer");
+  DLB_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0 && (uintptr_t)src % 16 == 0, DLB_ERR_INVALID,
+              "p2p_push_rows: rows must be multiples of 16 bytes and 16-byte aligned");
+  DLB_REQUIRE(world > 0 && world <= MAX_WORLD && my_rank >= 0 && my_rank < world && region_rows > 0, DLB_ERR_INVALID,
+              "p2p_push_rows: bad sizes");
+  PeerPtrs pd;
+  int rc = fill_peers(pd, peer_dst, world, "p2p_push_rows");
+  if (rc != DLB_OK) return rc;
+  const long long vpr = row_bytes / 16;
+  push_rows_kernel<<<grid_for((long long)world * region_rows * vpr), THREADS, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const uint4*>(src), vpr, counts, world, my_rank, region_rows, pd);
+  count_launch();
+  DLB_CHECK_LAUNCH("push_rows_kernel");
+  return DLB_OK;
+}

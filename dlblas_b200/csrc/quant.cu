@@ -139,11 +139,17 @@ __global__ void __launch_bounds__(THREADS) permute_rows_kernel(const uint4* __re
   for (long long u = (long long)blockIdx.x * THREADS + threadIdx.x; u < total; u += (long long)gridDim.x * THREADS) {
     const long long row = u / vec_per_row;
     const long long c = u - row * vec_per_row;
-    const uint4 v = __ldg(q + u);
-    const float s = (scales != nullptr && c < groups) ? __ldg(scales + row * groups + c) : 0.f;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    float s = 0.f;
+    bool loaded = false;               // rows without any destination are not read at all
     for (int j = 0; j < fanout; ++j) {
       const int d = __ldg(dst_pos + row * fanout + j);
       if (d < 0) continue;
+      if (!loaded) {
+        v = __ldg(q + u);
+        if (scales != nullptr && c < groups) s = __ldg(scales + row * groups + c);
+        loaded = true;
+      }
       out_q[(long long)d * vec_per_row + c] = v;
       if (scales != nullptr && c < groups) out_s[(long long)d * groups + c] = s;
     }
@@ -214,7 +220,7 @@ __global__ void __launch_bounds__(THREADS) silu_mul_quant_kernel(const T* __rest
 template <typename T, typename IdT>
 __global__ void __launch_bounds__(THREADS) sum_topk_kernel(const T* __restrict__ y, long long tokens, int top_k,
                                                            long long h, const IdT* __restrict__ ids, long long id_lo,
-                                                           long long id_hi, T* __restrict__ out) {
+                                                           long long id_hi, int skip_unrouted, T* __restrict__ out) {
   const long long vec_per_row = h / 8;
   const long long total = tokens * vec_per_row;
   for (long long u = (long long)blockIdx.x * THREADS + threadIdx.x; u < total; u += (long long)gridDim.x * THREADS) {
@@ -223,17 +229,19 @@ __global__ void __launch_bounds__(THREADS) sum_topk_kernel(const T* __restrict__
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    bool any = false;
     for (int j = 0; j < top_k; ++j) {
       if (ids != nullptr) {
         const long long id = (long long)ids[t * top_k + j];
         if (id < id_lo || id >= id_hi) continue;
       }
+      any = true;
       float v[8];
       Vec8<T>::load(y + (t * top_k + j) * h + c, v);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += v[i];
     }
-    Vec8<T>::store(out + t * h + c, acc);
+    if (any || !skip_unrouted) Vec8<T>::store(out + t * h + c, acc);   // rows nobody routed to: zeros, or left alone
   }
 }
 
@@ -445,15 +453,15 @@ extern "C" int dlb_silu_mul_quant(const void* gate_up, int dtype, int64_t rows, 
 namespace {
 template <typename T>
 int launch_sum_topk(const void* y, int64_t tokens, int top_k, int64_t h, const void* ids, int ids_dtype, int64_t lo,
-                    int64_t hi, void* out, cudaStream_t st) {
+                    int64_t hi, int skip, void* out, cudaStream_t st) {
   const int grid = grid_for(tokens * (h / 8));
   if (ids != nullptr && ids_dtype == DLB_I32)
     sum_topk_kernel<T, int><<<grid, THREADS, 0, st>>>(reinterpret_cast<const T*>(y), tokens, top_k, h,
-                                                     reinterpret_cast<const int*>(ids), lo, hi,
+                                                     reinterpret_cast<const int*>(ids), lo, hi, skip,
                                                      reinterpret_cast<T*>(out));
   else
     sum_topk_kernel<T, long long><<<grid, THREADS, 0, st>>>(reinterpret_cast<const T*>(y), tokens, top_k, h,
-                                                           reinterpret_cast<const long long*>(ids), lo, hi,
+                                                           reinterpret_cast<const long long*>(ids), lo, hi, skip,
                                                            reinterpret_cast<T*>(out));
   count_launch();
   DLB_CHECK_LAUNCH("sum_topk_kernel");
@@ -462,7 +470,8 @@ int launch_sum_topk(const void* y, int64_t tokens, int top_k, int64_t h, const v
 }  // namespace
 
 extern "C" int dlb_moe_sum_topk(const void* y, int dtype, int64_t tokens, int top_k, int64_t h, const void* ids,
-                                int ids_dtype, int64_t id_lo, int64_t id_hi, void* out, void* stream) {
+                                int ids_dtype, int64_t id_lo, int64_t id_hi, int skip_unrouted_rows, void* out,
+                                void* stream) {
   DLB_REQUIRE(tokens >= 0 && top_k > 0 && h > 0 && h % 8 == 0, DLB_ERR_INVALID,
               "sum_topk: h=%lld must be a positive multiple of 8", (long long)h);
   DLB_REQUIRE(ids == nullptr || ids_dtype == DLB_I32 || ids_dtype == DLB_I64, DLB_ERR_INVALID,
@@ -471,9 +480,11 @@ extern "C" int dlb_moe_sum_topk(const void* y, int dtype, int64_t tokens, int to
   DLB_REQUIRE(y && out, DLB_ERR_INVALID, "sum_topk: null pointer");
   DLB_REQUIRE((uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0, DLB_ERR_INVALID, "sum_topk: misaligned");
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == DLB_BF16) return launch_sum_topk<__nv_bfloat16>(y, tokens, top_k, h, ids, ids_dtype, id_lo, id_hi, out, st);
-  if (dtype == DLB_F16) return launch_sum_topk<__half>(y, tokens, top_k, h, ids, ids_dtype, id_lo, id_hi, out, st);
-  if (dtype == DLB_F32) return launch_sum_topk<float>(y, tokens, top_k, h, ids, ids_dtype, id_lo, id_hi, out, st);
+  const int skip = (ids != nullptr && skip_unrouted_rows) ? 1 : 0;
+  if (dtype == DLB_BF16)
+    return launch_sum_topk<__nv_bfloat16>(y, tokens, top_k, h, ids, ids_dtype, id_lo, id_hi, skip, out, st);
+  if (dtype == DLB_F16) return launch_sum_topk<__half>(y, tokens, top_k, h, ids, ids_dtype, id_lo, id_hi, skip, out, st);
+  if (dtype == DLB_F32) return launch_sum_topk<float>(y, tokens, top_k, h, ids, ids_dtype, id_lo, id_hi, skip, out, st);
   return fail(DLB_ERR_INVALID, "sum_topk: unsupported dtype %d", dtype);
 }
 

@@ -16,7 +16,7 @@ from ...kernels.moe import silu_and_mul_masked_post_quant_fwd
 from ...utils.logger import get_logger
 from ...utils.utils import DisposibleTensor
 from .kernels.blocked_fp8_fused_moe import _renormalize, moe_expert_forward
-from .token_dispatcher import TokenDispatcherLowLatency, TokenDispatcherNormal
+from .token_dispatcher import TokenDispatcherLowLatency, TokenDispatcherNormal, TokenDispatcherP2P
 
 logger = get_logger(__name__)
 
@@ -40,10 +40,26 @@ class FusedMoENormal:
                                                       num_local_experts=self.num_local_experts,
                                                       hidden_size=hidden_dim, params_dtype=out_dtype,
                                                       expert_alignment=expert_alignment)
+        # Exchange backend: "p2p" = in-kernel stores into the peers' memory (default with more than one
+        # rank), "nccl" = variable-size all-to-all.  DLBLAS_EP_MAX_TOKENS bounds the tokens per rank and call.
+        backend = os.environ.get("DLBLAS_EP_BACKEND", "p2p" if ep_size > 1 else "nccl").lower()
+        self.p2p_dispatcher = None
+        if backend == "p2p" and ep_size > 1:
+            self.p2p_dispatcher = TokenDispatcherP2P(
+                ep_group, num_experts, self.num_local_experts, hidden_dim, out_dtype,
+                max_tokens_per_rank=int(os.environ.get("DLBLAS_EP_MAX_TOKENS", "8192")), max_top_k=top_k)
 
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,
                 up_weights: torch.Tensor, up_scale: torch.Tensor, down_weights: torch.Tensor,
                 down_scale: torch.Tensor, expert_list: List[int] = None):
+        if self.p2p_dispatcher is not None:
+            d = self.p2p_dispatcher
+            hs = hidden_states.flatten(0, -2) if hidden_states.dim() > 2 else hidden_states
+            (rq, rs), rids, rw = d.dispatch_from_hidden(hs, topk_ids, topk_weights, self.block_size)
+            out_rows = moe_expert_forward(None, rq, rs, up_weights, up_scale, down_weights, down_scale, rw, rids,
+                                          topk_ids.shape[1], hidden_states.dtype, 0, self.num_local_experts,
+                                          _C.QUANT_DIV_EPS, skip_unrouted_rows=True)
+            return d.combine(out_rows).view(hidden_states.shape)
         # per_token_group_quant_fp8 fused with the packing of the send buffer (one pass over the tokens)
         x, recv_topk_ids, recv_topk_weights, recv_tokens_per_expert = self.token_dispatcher.dispatch_from_hidden(
             hidden_states.flatten(0, -2) if hidden_states.dim() > 2 else hidden_states, topk_ids, topk_weights,

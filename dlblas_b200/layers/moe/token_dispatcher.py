@@ -365,3 +365,121 @@ class TokenDispatcherLowLatency:
         ops.ep_gather(back, topk_idx.to(torch.int32).contiguous(), topk_weights.contiguous(),
                       plan.slot_pos.view(plan.num_tokens, -1), out)
         return out, _record_event(), (lambda: None)
+
+
+# ----------------------------------------------------------------------------------------------
+# normal (prefill) mode over peer-to-peer stores: no host synchronisation, no staging copies
+# ----------------------------------------------------------------------------------------------
+class TokenDispatcherP2P:
+    """Dispatch / combine through symmetric memory (`torch.distributed._symmetric_memory`): the
+    quantiser of the extension stores every token's FP8 row, scales and routing metadata directly
+    into the destination ranks' receive regions over NVLink, and the combine pushes result rows back
+    the same way (csrc/p2p.cu).  Two device-side barriers per layer order the pushes; split sizes
+    never travel to the host, so the layer runs without a CPU round trip.
+
+    Receive buffers hold `world` regions of `max_tokens_per_rank` rows; unused rows carry id -1 and
+    are skipped by the expert kernels.  All ranks must construct the dispatcher collectively."""
+
+    def __init__(self, group, num_experts: int, num_local_experts: int, hidden_size: int,
+                 params_dtype: torch.dtype = torch.bfloat16, max_tokens_per_rank: int = 8192, max_top_k: int = 8):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.num_experts = num_experts
+        self.num_local_experts = num_local_experts
+        self.hidden_size = hidden_size
+        self.params_dtype = params_dtype
+        self.world_size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        assert num_experts == num_local_experts * self.world_size, "experts must split evenly over the ranks"
+        assert hidden_size % 128 == 0 and params_dtype in (torch.bfloat16, torch.float16)
+        self.region_rows = int(max_tokens_per_rank)
+        self.kp = (max_top_k + 1) // 2 * 2
+        self.meta_ints = 2 * self.kp
+        w, h = self.world_size, hidden_size
+        rows = w * self.region_rows
+        self.rows = rows
+        dev = torch.device("cuda", torch.cuda.current_device())
+
+        def al(n):
+            return (n + 255) // 256 * 256
+
+        sizes = [("q", al(rows * h)), ("s", al(rows * (h // 128) * 4)), ("meta", al(rows * self.meta_ints * 4)),
+                 ("counts", 256), ("comb", al(rows * h * 2))]
+        offs, total = {}, 0
+        for name, n in sizes:
+            offs[name] = total
+            total += n
+        gname = group.group_name if hasattr(group, "group_name") else group
+        try:
+            if not symm_mem.is_symm_mem_enabled_for_group(gname):
+                symm_mem.enable_symm_mem_for_group(gname)
+        except Exception:      # newer torch enables groups on first rendezvous
+            pass
+        self._buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        self._hdl = symm_mem.rendezvous(self._buf, gname)
+        bases = [int(p) for p in self._hdl.buffer_ptrs]
+        self._peers = {name: (ctypes.c_void_p * w)(*[b + offs[name] for b in bases]) for name, _ in sizes}
+        b = self._buf
+        self.recv_q = b[offs["q"]: offs["q"] + rows * h].view(ops.FP8).view(rows, h)
+        self.recv_s = b[offs["s"]: offs["s"] + rows * (h // 128) * 4].view(torch.float32).view(rows, h // 128)
+        self.recv_meta = b[offs["meta"]: offs["meta"] + rows * self.meta_ints * 4].view(torch.int32).view(rows, -1)
+        self.recv_counts = b[offs["counts"]: offs["counts"] + 256].view(torch.int32)
+        self.comb = b[offs["comb"]: offs["comb"] + rows * h * 2].view(params_dtype).view(rows, h)
+        self.recv_counts.zero_()
+        self._hdl.barrier(channel=0)
+        self.handle = None
+        self.hidden_shape = None
+
+    def dispatch_from_hidden(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+                             block_size: int = 128):
+        """Returns ((recv_q, recv_s), recv_ids, recv_weights): `world * max_tokens_per_rank` rows, local
+        expert ids with -1 for unused rows and for slots owned by other ranks."""
+        assert block_size == 128
+        t, k = topk_idx.shape
+        assert t <= self.region_rows, f"{t} tokens exceed max_tokens_per_rank={self.region_rows}"
+        assert k <= self.kp
+        w, dev = self.world_size, hidden_states.device
+        self.hidden_shape = hidden_states.shape
+        dest = ops.ep_dest_ranks(topk_idx.contiguous(), self.num_local_experts, w)
+        _, _, _, within, counts = ops.sort_by_expert(dest, w, want_rank=True, want_counts=True)
+        meta = torch.zeros(t, self.meta_ints, dtype=torch.int32, device=dev)
+        meta[:, :k] = topk_idx
+        meta[:, self.kp:self.kp + k] = topk_weights.to(torch.float32).view(torch.int32)
+        p = self._peers
+        _C.check(_C.lib().dlb_p2p_quant_push(
+            _C.ptr(hidden_states), _C.dtype_code(hidden_states.dtype), t, hidden_states.shape[1],
+            hidden_states.stride(0), _C.QUANT_DIV_EPS, 1e-10, _C.ptr(within), w, self.rank, self.region_rows,
+            p["q"], p["s"], p["meta"], _C.ptr(meta), self.meta_ints, p["counts"], _C.ptr(counts), _C.stream(dev)))
+        self._hdl.barrier(channel=0)
+        recv_ids = torch.empty(self.rows, k, dtype=torch.int64, device=dev)
+        recv_w = torch.empty(self.rows, k, dtype=torch.float32, device=dev)
+        _C.check(_C.lib().dlb_p2p_unpack_meta(_C.ptr(self.recv_meta), self.meta_ints, k, _C.ptr(self.recv_counts), w,
+                                             self.region_rows, self.rank * self.num_local_experts,
+                                             self.num_local_experts, _C.ptr(recv_ids), _C.ptr(recv_w), _C.stream(dev)))
+        self.handle = (within.view(t, w), t)
+        return (self.recv_q, self.recv_s), recv_ids, recv_w
+
+    def combine(self, out_rows: torch.Tensor) -> torch.Tensor:
+        """out_rows: [world * max_tokens_per_rank, H] results for the received rows (unused rows ignored)."""
+        within, t = self.handle
+        w, dev = self.world_size, out_rows.device
+        assert out_rows.is_contiguous() and out_rows.shape == (self.rows, self.hidden_size)
+        assert out_rows.dtype == self.comb.dtype
+        _C.check(_C.lib().dlb_p2p_push_rows(_C.ptr(out_rows), self.hidden_size * out_rows.element_size(),
+                                           _C.ptr(self.recv_counts), w, self.rank, self.region_rows,
+                                           self._peers["comb"], _C.stream(dev)))
+        self._hdl.barrier(channel=1)
+        base = (torch.arange(w, device=dev, dtype=torch.int32) * self.region_rows)[None, :]
+        idx = torch.where(within >= 0, within + base, torch.full_like(within, -1)).contiguous()
+        ones = torch.ones(t, w, dtype=torch.float32, device=dev)
+        out = torch.empty(t, self.hidden_size, dtype=out_rows.dtype, device=dev)
+        # out[t] = sum over the ranks the token visited, in rank order (fp32 accumulation)
+        ops.ep_gather(self.comb, idx, ones, idx, out)
+        self.handle = None
+        return out.view(self.hidden_shape)
+
+    def release(self):
+        self.handle = None
+        return True

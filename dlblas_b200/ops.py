@@ -176,7 +176,7 @@ def grouped_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch
 
 # --------------------------------------------------------------------------- combine
 def sum_topk(y: torch.Tensor, tokens: int, top_k: int, ids: Optional[torch.Tensor] = None, id_lo: int = 0,
-             id_hi: int = 0) -> torch.Tensor:
+             id_hi: int = 0, skip_unrouted_rows: bool = False) -> torch.Tensor:
     """out[t] = sum_j y[t*top_k + j]; with ids, slots whose id is outside [id_lo, id_hi) are skipped."""
     require_cuda(y)
     assert y.is_contiguous()
@@ -186,8 +186,8 @@ def sum_topk(y: torch.Tensor, tokens: int, top_k: int, ids: Optional[torch.Tenso
     if ids is not None:
         assert ids.is_contiguous()
         idt = dtype_code(ids.dtype)
-    check(lib().dlb_moe_sum_topk(ptr(y), dtype_code(y.dtype), tokens, top_k, h, ptr(ids), idt, id_lo, id_hi, ptr(out),
-                                 stream(y.device)))
+    check(lib().dlb_moe_sum_topk(ptr(y), dtype_code(y.dtype), tokens, top_k, h, ptr(ids), idt, id_lo, id_hi,
+                                 int(skip_unrouted_rows), ptr(out), stream(y.device)))
     return out
 
 

@@ -167,9 +167,10 @@ DLB_API int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a
  * out[t, :] = cast(sum_j y[t*top_k + j, :]) with fp32 accumulation in slot order: the
  * `intermediate_cache2.sum(dim=1)` of dlblas/layers/moe/kernels/blocked_fp8_fused_moe.py:337.
  * ids (may be NULL; int32/int64 [tokens*top_k]): slots whose id is outside [id_lo, id_hi) count as
- * zero rows and are not read (the reference zero-fills them instead, :291, :317). */
+ * zero rows and are not read (the reference zero-fills them instead, :291, :317).  skip_unrouted_rows != 0:
+ * a token none of whose slots is in range is not written at all (padding rows of a receive buffer). */
 DLB_API int dlb_moe_sum_topk(const void* y, int dtype, int64_t tokens, int top_k, int64_t h, const void* ids,
-                     int ids_dtype, int64_t id_lo, int64_t id_hi, void* out, void* stream);
+                     int ids_dtype, int64_t id_lo, int64_t id_hi, int skip_unrouted_rows, void* out, void* stream);
 /* ep_gather (dlblas/kernels/fused_moe_v3.py:159-233): out[t] = sum_j w[t,j] * in[index[t,j]] over
  * slots with ids[t,j] >= 0, fp32 accumulation in slot order.  ids/index: int32 or int64 (idx_dtype). */
 DLB_API int dlb_ep_gather(const void* in, int dtype, int64_t h, const void* ids, const void* index, int idx_dtype,
@@ -190,6 +191,30 @@ DLB_API int dlb_ep_scatter(const void* x, int64_t row_bytes, const float* x_scal
  * with dlb_sort_by_expert(num_experts = world) yields every (token, rank) pair's row in the send buffer. */
 DLB_API int dlb_ep_dest_ranks(const void* ids, int ids_dtype, int64_t tokens, int top_k, int num_local_experts,
                       int world, int32_t* dest, void* stream);
+
+/* ---- expert-parallel exchange by peer-to-peer stores ------------------------------------------
+ * In-kernel replacement of deep_ep.Buffer.dispatch / combine (dlblas/layers/moe/token_dispatcher.py:345,
+ * 427) for GPUs of one NVLink domain.  Every rank holds receive buffers of `world` regions of
+ * `region_rows` rows (region s = rows sent by rank s); peer_* are arrays of `world` device pointers to
+ * the same buffer on every rank (symmetric allocation).  The caller puts a cross-rank barrier on the
+ * stream after each push before the destination reads.
+ * dlb_p2p_quant_push: per_token_group_quant_fp8 arithmetic (mode/eps as in dlb_quant_fp8, groups of 128)
+ *   fused with the dispatch: token t's e4m3 row, scales and `meta_ints` int32 of metadata are stored into
+ *   region my_rank, row within[t*world + r], of every rank r with within >= 0; counts[r] (rows sent to r)
+ *   is stored into peer_counts[r][my_rank].
+ * dlb_p2p_unpack_meta: on the receiver, metadata rows (top_k global ids, then at int offset meta_ints/2 the
+ *   top_k weights' bit patterns) -> local ids int64 (-1 for other ranks' experts and unused rows) + weights.
+ * dlb_p2p_push_rows: combine direction; row j < counts[s] of region s goes to rank s, region my_rank, row j. */
+DLB_API int dlb_p2p_quant_push(const void* x, int x_dtype, int64_t tokens, int64_t k, int64_t ldx, int mode, float eps,
+                       const int32_t* within, int world, int my_rank, int64_t region_rows,
+                       const void* const* peer_q, const void* const* peer_scales, const void* const* peer_meta,
+                       const int32_t* meta, int meta_ints, const void* const* peer_counts, const int32_t* counts,
+                       void* stream);
+DLB_API int dlb_p2p_unpack_meta(const int32_t* meta, int meta_ints, int top_k, const int32_t* counts, int world,
+                        int64_t region_rows, int expert_lo, int num_local_experts, int64_t* ids, float* weights,
+                        void* stream);
+DLB_API int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32_t* counts, int world, int my_rank,
+                      int64_t region_rows, const void* const* peer_dst, void* stream);
 
 /* ---- routing -------------------------------------------------------------------
  * topk(softmax(logits, fp32), k) with lowest-index tie-break, optional w / sum(w): the routing the

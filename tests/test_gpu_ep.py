@@ -41,12 +41,16 @@ def _worker(rank, world, port, ret):
         ref = O.moe_layer(x, ow, oids, w13, w13s, w2, w2s, top_k=k)
         sl = slice(rank * nle, (rank + 1) * nle)
         local = [w13[sl].to(dev), w13s[sl].to(dev), w2[sl].to(dev), w2s[sl].to(dev)]
-        for low_latency in (False, True):
+        os.environ["DLBLAS_EP_MAX_TOKENS"] = "256"
+        for backend, low_latency in (("p2p", False), ("nccl", False), ("nccl", True)):
+            os.environ["DLBLAS_EP_BACKEND"] = backend
             layer = build_deepep_moe(low_latency, world, dist.group.WORLD, e, h, 128, k, torch.bfloat16)
-            out = layer.forward(x.to(dev), ow.to(dev), oids.to(dev), *local)
+            assert (getattr(layer, "p2p_dispatcher", None) is not None) == (backend == "p2p")
+            for _ in range(3):                      # repeated steps reuse the symmetric buffers
+                out = layer.forward(x.to(dev), ow.to(dev), oids.to(dev), *local)
             _C.check_status(dev)
             err = O.rel_frobenius(out.cpu(), ref)
-            assert out.shape == (t, h) and err < 2e-2, (low_latency, err)
+            assert out.shape == (t, h) and err < 2e-2, (backend, low_latency, err)
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()
