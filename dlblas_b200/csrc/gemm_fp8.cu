@@ -1,20 +1,25 @@
 // Block-scaled FP8 (e4m3) GEMMs for sm_100a: dense and grouped over ragged expert
 // segments.  One persistent, warp-specialised kernel:
 //
-//   warp 16 (1 lane)    TMA producer: A tile [128 x 128B] and B tile [BN x 128B] per
+//   warp 8  (1 thread)  TMA producer: A tile [128 x 128B] and B tile [BN x 128B] per
 //                       128-wide K block into a ring of 128B-swizzled smem stages.
-//   warp 17 (1 lane)    issues tcgen05.mma kind::f8f6f4 (128 x BN x 32, four per K block)
+//   warp 9  (1 thread)  issues tcgen05.mma kind::f8f6f4 (128 x BN x 32, four per K block)
 //                       into a ring of TMEM accumulators, one accumulator per K block.
-//   warps 0-15          promotion + epilogue: tcgen05.ld each K block's partial product,
+//   warps 0-7           promotion + epilogue: tcgen05.ld each K block's partial product,
 //                       acc += partial * a_scale[row, kb] * b_scale[nblk, kb] on the CUDA
 //                       cores (the scales are arbitrary fp32, so the hardware block-scale
 //                       path, which wants UE8M0 scales, does not apply), then the epilogue.
-//   warp 16 / warp 17   TMA producer / MMA issuer (see below).
+//   warps 10-11         idle; they complete the third warpgroup so that it can hand its
+//                       registers to the promotion warpgroups (setmaxnreg).
 //
-// Per 128 x 256 x 128 K block the tensor pipe needs ~540 cycles and the promotion 32768 FMAs
-// plus 128 KB of TMEM reads, i.e. half of the SM's FP32 rate: the promotion is spread over 16
-// warps (four per scheduler partition) because two warps per partition reach only half of the
-// FP32 issue rate and leave every TMEM load latency exposed.
+// (A 16-warp variant, four promotion warps per scheduler partition with 64 accumulator columns
+// each, was measured too: 5 % faster on large dense problems, but its 96-register budget spills
+// in the fused silu*up epilogue and it was 15 % slower on the grouped w13 GEMM, so the 8-warp
+// layout below is the one kept.)
+//
+// Register budget: an accumulator tile is 128 x BN fp32 = half of the register file at
+// BN = 256, and hiding the TMEM load latency needs 64 more staging registers per promotion
+// thread, so the promotion warpgroups run at 232 registers and the third warpgroup at 40.
 //
 // The arithmetic follows dlblas/kernels/fp8_gemm.py:50-59 and
 // dlblas/layers/moe/kernels/blocked_fp8_fused_moe.py:95-156 of the reference: fp32
@@ -33,10 +38,12 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 128;              // bytes == elements (e4m3)
 constexpr int A_STAGE_BYTES = BM * BK;
-constexpr int EPI_WARPS = 16;        // four warpgroups of promotion warps
-constexpr int PRODUCER_WARP = 16;
-constexpr int MMA_WARP = 17;
-constexpr int NUM_THREADS = 576;     // 18 warps, 112 registers each
+constexpr int EPI_WARPS = 8;         // two warpgroups
+constexpr int PRODUCER_WARP = 8;
+constexpr int MMA_WARP = 9;
+constexpr int NUM_THREADS = 384;      // three warpgroups
+constexpr int REGS_PROMOTION = 232;    // 256 * 232 + 128 * 40 = 384 * 168
+constexpr int REGS_OTHER = 40;
 constexpr int TMEM_COLS = 512;
 
 struct GemmArgs {
@@ -47,7 +54,7 @@ struct GemmArgs {
   void* c;
   long long ldc;
   float* q_scale;             // SWIGLU_QUANT: [rows, n_half/128]
-  int quant_mode;             // SWIGLU_QUANT: DLB_QUANT_RECIP_MUL or DLB_QUANT_DIV_EPS
+  int quant_mode;
   float quant_eps;
   const int4* tiles;          // nullptr: dense, M tiles derived from m
   int m, n, k;
@@ -142,24 +149,36 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint
       : "memory");
 }
 
-// 32 lanes x 16 consecutive columns, one fp32 per register.
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+// 32 lanes x 32 consecutive columns, one fp32 per register.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
       : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr)
       : "memory");
 }
-// Waits for this thread's outstanding tcgen05.ld.  The staging registers are listed as
+// Waits for all of this thread's outstanding tcgen05.ld.  Both staging buffers are listed as
 // read-write operands so the compiler cannot schedule arithmetic on them above the wait.
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[16]) {
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[32], uint32_t (&b)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
-                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+               : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
+                 "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]),
+                 "+r"(a[16]), "+r"(a[17]), "+r"(a[18]), "+r"(a[19]), "+r"(a[20]), "+r"(a[21]), "+r"(a[22]),
+                 "+r"(a[23]), "+r"(a[24]), "+r"(a[25]), "+r"(a[26]), "+r"(a[27]), "+r"(a[28]), "+r"(a[29]),
+                 "+r"(a[30]), "+r"(a[31]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]),
+                 "+r"(b[6]), "+r"(b[7]), "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]),
+                 "+r"(b[14]), "+r"(b[15]), "+r"(b[16]), "+r"(b[17]), "+r"(b[18]), "+r"(b[19]), "+r"(b[20]),
+                 "+r"(b[21]), "+r"(b[22]), "+r"(b[23]), "+r"(b[24]), "+r"(b[25]), "+r"(b[26]), "+r"(b[27]),
+                 "+r"(b[28]), "+r"(b[29]), "+r"(b[30]), "+r"(b[31])
                :
                : "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait_plain() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Two fp32 FMAs per instruction (sm_100): d.xy = a.xy * b.xy + d.xy on packed register pairs.
 __device__ __forceinline__ void fma2(uint64_t& d, uint32_t a_lo, uint32_t a_hi, uint64_t b) {
@@ -174,6 +193,13 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
 }
 __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+template <int N> __device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
@@ -197,12 +223,13 @@ template <int BN> struct Cfg {
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TMEM_BUFS = TMEM_COLS / BN;
+  static constexpr int SEG = BN / 4;  // columns per thread segment (two segments per thread)
   // dynamic smem: stages | barriers (full, empty, tmem_full, tmem_empty) | misc
   static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 2 * TMEM_BUFS + 2;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
-  static constexpr int XCHG_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // 2 tiles x 4 column groups x 128 floats
-  static constexpr int SMEM_BYTES = XCHG_OFF + 8 * BM * 4 + 1024;  // + slack for 1024 B alignment
+  static constexpr int XCHG_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // 2 tiles x 2 warpgroups x 128 floats
+  static constexpr int SMEM_BYTES = XCHG_OFF + 4 * BM * 4 + 1024;  // + slack for 1024 B alignment
 };
 
 struct Tile {
@@ -323,6 +350,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp >= EPI_WARPS) {
+    // third warpgroup: give registers away, then run the producer / MMA roles
+    reg_dec<REGS_OTHER>();
   // The producer and MMA warps run their loops with all 32 lanes converged and elect one lane
   // only around the TMA / tcgen05 instructions: addresses, descriptors and barrier operands then
   // live in uniform registers.  With a single lane running the whole loop the same instructions
@@ -406,23 +435,20 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   }
   } else {
     // ---- promotion + epilogue warps ------------------------------------------
-    // 16 warps: warp w drains TMEM lanes [32 (w & 3), +32) and 64 accumulator columns (column
-    // group cg = w >> 2).  Four warps per scheduler partition instead of two doubles the FP32
-    // issue rate the SM sustains and lets one warp's TMEM load latency hide behind the FMAs of
-    // the others; the price is a 112-register budget (64 accumulators + 16 staging).
-    const int cg = warp >> 2;                 // column group 0..3
+    reg_inc<REGS_PROMOTION>();
+    const int wg = warp >> 2;                 // 0 or 1
     const int quad = warp & 3;                // TMEM lane quadrant of this warp
     const int r = quad * 32 + lane;           // row inside the tile
-    constexpr int COLS = BN / 4;              // accumulator columns per thread: 64 or 32
-    constexpr int CH = COLS / 16;             // 16-column chunks per K block
-    // TMEM column of chunk c.  SWIGLU_QUANT: chunks 0..1 are gate columns [32 cg, +32), chunks
-    // 2..3 the matching up columns 128 + [32 cg, +32).  Otherwise 64 (32) contiguous columns.
-    auto chunk_col = [&](int c) -> uint32_t {
-      if constexpr (MODE == DLB_EPI_SWIGLU_QUANT)
-        return (uint32_t)((c < CH / 2) ? cg * (COLS / 2) + c * 16 : BN / 2 + cg * (COLS / 2) + (c - CH / 2) * 16);
-      else
-        return (uint32_t)(cg * COLS + c * 16);
-    };
+    constexpr int SEG = C::SEG;
+    // TMEM column offsets of this thread's two segments, and matching output columns
+    int seg_col[2];
+    if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
+      seg_col[0] = wg * SEG;                  // gate columns
+      seg_col[1] = BN / 2 + wg * SEG;         // up columns
+    } else {
+      seg_col[0] = wg * 2 * SEG;
+      seg_col[1] = wg * 2 * SEG + SEG;
+    }
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     uint32_t it = 0;
     uint32_t tile_no = 0;
@@ -432,23 +458,27 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const bool row_ok = r < ti.rows;
       const long long p = (long long)ti.row0 + r;          // row of A / sorted position
       const float* as_ptr = g.a_s + (row_ok ? p : (long long)ti.row0) * g.a_s_rs;
-      // weight-scale rows of this thread's columns (two for the gate / up halves)
-      const float* bs0;
-      const float* bs1;
+      // scale blocks of the two segments
+      const float* bs_ptr[2];
       {
         const float* be = g.b_s + (long long)ti.e * g.b_s_es;
+        int nb0, nb1;
         if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
-          bs0 = be + (long long)(ti.n0 / 128) * kblocks;
-          bs1 = be + (long long)((g.n_half + ti.n0) / 128) * kblocks;
+          nb0 = ti.n0 / 128;
+          nb1 = (g.n_half + ti.n0) / 128;
         } else {
+          nb0 = (ti.n0 + seg_col[0]) / 128;
+          nb1 = (ti.n0 + seg_col[1]) / 128;
           const int nb_max = (g.n + 127) / 128 - 1;
-          bs0 = be + (long long)min((ti.n0 + cg * COLS) / 128, nb_max) * kblocks;
-          bs1 = bs0;
+          nb0 = min(nb0, nb_max);
+          nb1 = min(nb1, nb_max);
         }
+        bs_ptr[0] = be + (long long)nb0 * kblocks;
+        bs_ptr[1] = be + (long long)nb1 * kblocks;
       }
-      uint64_t acc2[COLS / 2];            // COLS fp32 accumulators, packed in pairs
+      uint64_t acc2[SEG];                 // 2 * SEG fp32 accumulators, packed in pairs
 #pragma unroll
-      for (int j = 0; j < COLS / 2; ++j) acc2[j] = 0ull;
+      for (int j = 0; j < SEG; ++j) acc2[j] = 0ull;
       // row / weight of the scatter epilogue, fetched now so that the two dependent loads are
       // long done when the tile's last K block arrives
       long long crow = p;
@@ -459,87 +489,132 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           row_w = g.weights[crow];
         }
       }
-      // scales one K block ahead
-      float a_sc = __ldg(as_ptr), b_sc0 = __ldg(bs0), b_sc1 = b_sc0;
-      if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) b_sc1 = __ldg(bs1);
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+
+      // scales are fetched two K blocks ahead: under full TMA load an L2 round trip can take
+      // longer than one K block
+      float a_sc = __ldg(as_ptr), b_sc0 = __ldg(bs_ptr[0]), b_sc1 = __ldg(bs_ptr[1]);
+      float a_n1 = 0.f, b0_n1 = 0.f, b1_n1 = 0.f;
+      if (kblocks > 1) {
+        a_n1 = __ldg(as_ptr + g.a_s_ks);
+        b0_n1 = __ldg(bs_ptr[0] + 1);
+        b1_n1 = __ldg(bs_ptr[1] + 1);
+      }
+      // Two 32-column staging buffers.  A K block is drained in NB batches of two loads; the
+      // loads of the next batch (or of the next K block's first batch) are issued as soon as a
+      // staging buffer has been folded into the accumulators, so a load is always in flight.
+      constexpr int CH = 2 * SEG / 32;   // 32-column chunks per thread and K block (2 or 4)
+      constexpr int NB = CH / 2;
+      auto chunk_col = [&](int c) { return (c * 32 < SEG) ? seg_col[0] + c * 32 : seg_col[1] + c * 32 - SEG; };
+      uint32_t s0[32], s1[32];
+      bool pending = false;              // first batch of the current K block already issued
+      for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
         const int b = it % C::TMEM_BUFS;
         const uint32_t buf_addr = lane_addr + (uint32_t)(b * BN);
-        float a_nx = 0.f, b_nx0 = 0.f, b_nx1 = 0.f;
-        if (kb + 1 < kblocks) {
-          a_nx = __ldg(as_ptr + (long long)(kb + 1) * g.a_s_ks);
-          b_nx0 = __ldg(bs0 + kb + 1);
-          if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) b_nx1 = __ldg(bs1 + kb + 1);
+        float a_n2 = 0.f, b0_n2 = 0.f, b1_n2 = 0.f;
+        if (kb + 2 < kblocks) {
+          a_n2 = __ldg(as_ptr + (long long)(kb + 2) * g.a_s_ks);
+          b0_n2 = __ldg(bs_ptr[0] + kb + 2);
+          b1_n2 = __ldg(bs_ptr[1] + kb + 2);
         }
-        if (!mbar_wait(tfull_bar(b), (it / C::TMEM_BUFS) & 1u, abort_flag, limit)) {
-          ok = false;
-          break;
+        if (!pending) {
+          if (!mbar_wait(tfull_bar(b), (it / C::TMEM_BUFS) & 1u, abort_flag, limit)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          tmem_ld32(buf_addr + chunk_col(0), s0);
+          tmem_ld32(buf_addr + chunk_col(1), s1);
         }
-        tc_fence_after();
-        uint32_t st[16];
-        tmem_ld16(buf_addr + chunk_col(0), st);
-        const float sc0f = a_sc * b_sc0;
+        pending = false;
+        const float sc0f = a_sc * b_sc0, sc1f = a_sc * b_sc1;
         const uint64_t sc0 = pack2(sc0f, sc0f);
-        uint64_t sc1 = sc0;
-        if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
-          const float sc1f = a_sc * b_sc1;
-          sc1 = pack2(sc1f, sc1f);
-        }
+        const uint64_t sc1 = pack2(sc1f, sc1f);
+        const bool has_next = kb + 1 < kblocks;
+        const int nb_buf = (it + 1) % C::TMEM_BUFS;
+        const uint32_t next_addr = lane_addr + (uint32_t)(nb_buf * BN);
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          tmem_ld_wait(st);
-          if (c == CH - 1) {
-            // every column of this accumulator that this warp owns is in registers
+        for (int q = 0; q < NB; ++q) {
+          tmem_ld_wait(s0, s1);
+          const bool last = (q == NB - 1);
+          if (last) {
+            // every column of this accumulator is in registers: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(b));
           }
-          const uint64_t sc = (MODE == DLB_EPI_SWIGLU_QUANT && c >= CH / 2) ? sc1 : sc0;
+          {
+            const uint64_t sc = ((2 * q) * 32 < SEG) ? sc0 : sc1;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) fma2(acc2[c * 8 + j], st[2 * j], st[2 * j + 1], sc);
-          if (c + 1 < CH) tmem_ld16(buf_addr + chunk_col(c + 1), st);
+            for (int j = 0; j < 16; ++j) fma2(acc2[(2 * q) * 16 + j], s0[2 * j], s0[2 * j + 1], sc);
+          }
+          if (!last) {
+            tmem_ld32(buf_addr + chunk_col(2 * q + 2), s0);
+          } else if (has_next) {
+            if (!mbar_wait(tfull_bar(nb_buf), ((it + 1) / C::TMEM_BUFS) & 1u, abort_flag, limit)) {
+              ok = false;
+            } else {
+              tc_fence_after();
+              tmem_ld32(next_addr + chunk_col(0), s0);
+            }
+          }
+          {
+            const uint64_t sc = ((2 * q + 1) * 32 < SEG) ? sc0 : sc1;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) fma2(acc2[(2 * q + 1) * 16 + j], s1[2 * j], s1[2 * j + 1], sc);
+          }
+          if (!last) {
+            tmem_ld32(buf_addr + chunk_col(2 * q + 3), s1);
+          } else if (has_next && ok) {
+            tmem_ld32(next_addr + chunk_col(1), s1);
+            pending = true;
+          }
         }
-        a_sc = a_nx;
-        b_sc0 = b_nx0;
-        b_sc1 = b_nx1;
+        if (!ok) {
+          tmem_ld_wait_plain();
+          break;
+        }
+        a_sc = a_n1;
+        b_sc0 = b0_n1;
+        b_sc1 = b1_n1;
+        a_n1 = a_n2;
+        b0_n1 = b0_n2;
+        b1_n1 = b1_n2;
       }
       if (!ok) break;
 
       // ---- epilogue ---------------------------------------------------------
-      float acc[COLS];
+      float acc[2 * SEG];
 #pragma unroll
-      for (int j = 0; j < COLS / 2; ++j) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
+      for (int j = 0; j < SEG; ++j) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
       if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
         // reference rounding points: GEMM1 output -> OutT, silu(gate)*up -> OutT, then
         // scale = absmax * (1/448), q = h / scale (dlblas/kernels/moe.py:398-417).
-        constexpr int OUTS = COLS / 2;      // 32 outputs per thread
-        float h[OUTS];
+        float h[SEG];
         float amax = 0.f;
 #pragma unroll
-        for (int j = 0; j < OUTS; ++j) {
+        for (int j = 0; j < SEG; ++j) {
           const float gt = to_f32<OutT>(from_f32<OutT>(acc[j]));
-          const float up = to_f32<OutT>(from_f32<OutT>(acc[OUTS + j]));
+          const float up = to_f32<OutT>(from_f32<OutT>(acc[SEG + j]));
           const float sv = gt / (1.f + __expf(-gt));
           h[j] = to_f32<OutT>(from_f32<OutT>(sv * up));
           amax = fmaxf(amax, fabsf(h[j]));
         }
-        // the four column groups hold the four quarters of each row's 128-wide quantisation
-        // group: exchange the partial maxima through smem (double-buffered by tile parity,
-        // one bounded barrier phase per tile)
-        float* xb = xchg + (tile_no & 1u) * 4 * BM;
-        xb[cg * BM + r] = amax;
+        // the two warpgroups hold the two halves of each row's 128-wide quantisation group:
+        // exchange the partial maxima through smem (double-buffered by tile parity, one
+        // bounded barrier phase per tile)
+        float* xb = xchg + (tile_no & 1u) * 2 * BM;
+        xb[wg * BM + r] = amax;
         mbar_arrive(xchg_bar);
         if (!mbar_wait(xchg_bar, tile_no & 1u, abort_flag, limit)) {
           ok = false;
           break;
         }
-        amax = fmaxf(fmaxf(xb[r], xb[BM + r]), fmaxf(xb[2 * BM + r], xb[3 * BM + r]));
-        const float scale = g.quant_mode == DLB_QUANT_RECIP_MUL ? amax * (1.0f / 448.0f)
-                                                                : fmaxf(amax, g.quant_eps) / 448.0f;
+        amax = fmaxf(amax, xb[(wg ^ 1) * BM + r]);
+        const float scale = g.quant_mode == DLB_QUANT_RECIP_MUL ? amax * (1.0f / 448.0f) : fmaxf(amax, g.quant_eps) / 448.0f;
         if (row_ok) {
-          uint8_t* dst = reinterpret_cast<uint8_t*>(g.c) + p * g.ldc + ti.n0 + cg * OUTS;
+          uint8_t* dst = reinterpret_cast<uint8_t*>(g.c) + p * g.ldc + ti.n0 + wg * SEG;
 #pragma unroll
-          for (int j = 0; j < OUTS; j += 16) {
+          for (int j = 0; j < SEG; j += 16) {
             uint32_t w[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -549,18 +624,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             }
             *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          if (cg == 0) g.q_scale[p * (long long)(g.n_half / 128) + ti.n0 / 128] = scale;
+          if (wg == 0) g.q_scale[p * (long long)(g.n_half / 128) + ti.n0 / 128] = scale;
         }
       } else {
         if (row_ok) {
           if constexpr (MODE == DLB_EPI_SCATTER_WEIGHT) {
 #pragma unroll
-            for (int j = 0; j < COLS; ++j) acc[j] *= row_w;
+            for (int j = 0; j < 2 * SEG; ++j) acc[j] *= row_w;
           }
-          const int col0 = ti.n0 + cg * COLS;
+          const int col0 = ti.n0 + seg_col[0];
           OutT* dst = reinterpret_cast<OutT*>(g.c) + crow * g.ldc + col0;
-          const int ncols = min(COLS, g.n - col0);   // n % 8 == 0
-          store_row<OutT, COLS>(dst, acc, ncols);
+          const int ncols = min(2 * SEG, g.n - col0);   // n % 8 == 0
+          store_row<OutT, 2 * SEG>(dst, acc, ncols);
         }
       }
     }
