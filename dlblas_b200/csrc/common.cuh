@@ -66,6 +66,20 @@ __device__ __forceinline__ uint16_t f32x2_to_e4m3x2(float lo, float hi) {
   return r;
 }
 
+// silu for the fused silu*up + quantise paths: fast exponential and a 2-ulp divide.  The result
+// is multiplied by `up` and rounded to a 16-bit type straight away, so the extra fp32 error only
+// shows where the product sits within 2 ulp of a 16-bit rounding boundary.
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+
+// Eight values times the reciprocal of their group's scale -> eight e4m3 bytes.  `inv` is the
+// correctly rounded 1 / scale; v * inv is within one fp32 ulp of v / scale.
+__device__ __forceinline__ uint2 quant8_rcp(const float (&v)[8], float inv) {
+  uint2 r;
+  r.x = (uint32_t)f32x2_to_e4m3x2(v[0] * inv, v[1] * inv) | ((uint32_t)f32x2_to_e4m3x2(v[2] * inv, v[3] * inv) << 16);
+  r.y = (uint32_t)f32x2_to_e4m3x2(v[4] * inv, v[5] * inv) | ((uint32_t)f32x2_to_e4m3x2(v[6] * inv, v[7] * inv) << 16);
+  return r;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -5,12 +5,17 @@
 //                       128-wide K block into a ring of 128B-swizzled smem stages.
 //   warp 9  (1 thread)  issues tcgen05.mma kind::f8f6f4 (128 x BN x 32, four per K block)
 //                       into a ring of TMEM accumulators, one accumulator per K block.
-//   warps 0-7           promotion + epilogue: tcgen05.ld each K block's partial product,
+//   warps 0-7           promotion: tcgen05.ld each K block's partial product,
 //                       acc += partial * a_scale[row, kb] * b_scale[nblk, kb] on the CUDA
 //                       cores (the scales are arbitrary fp32, so the hardware block-scale
-//                       path, which wants UE8M0 scales, does not apply), then the epilogue.
-//   warps 10-11         idle; they complete the third warpgroup so that it can hand its
-//                       registers to the promotion warpgroups (setmaxnreg).
+//                       path, which wants UE8M0 scales, does not apply).  At the end of a tile
+//                       they round the accumulators to the 16-bit output type, park them in a
+//                       shared-memory staging tile and go straight on to the next tile.
+//   warps 10-11         epilogue: rows of the staging tile leave with one bulk copy each
+//                       (store / scatter), or are turned into silu(gate)*up, quantised per 128
+//                       columns and stored as e4m3 (fused w13 epilogue), while the other roles
+//                       already work on the next tile.  (With fp32 output the tile does not fit
+//                       the staging buffer and the promotion warps store it themselves.)
 //
 // (A 16-warp variant, four promotion warps per scheduler partition with 64 accumulator columns
 // each, was measured too: 5 % faster on large dense problems, but its 96-register budget spills
@@ -41,6 +46,8 @@ constexpr int A_STAGE_BYTES = BM * BK;
 constexpr int EPI_WARPS = 8;         // two warpgroups
 constexpr int PRODUCER_WARP = 8;
 constexpr int MMA_WARP = 9;
+constexpr int STORE_WARP0 = 10;       // warps 10 and 11: epilogue out of the staging tile
+constexpr int STORE_WARPS = 2;
 constexpr int NUM_THREADS = 384;      // three warpgroups
 constexpr int REGS_PROMOTION = 232;    // 256 * 232 + 128 * 40 = 384 * 168
 constexpr int REGS_OTHER = 40;
@@ -195,6 +202,19 @@ __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
 
+// One row of the staging tile -> global memory, asynchronously (both addresses 16-byte aligned,
+// size a multiple of 16).
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(__cvta_generic_to_global(gdst)), "r"(ssrc), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all earlier bulk stores of this thread have read their shared-memory source
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all earlier bulk stores of this thread are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 template <int N> __device__ __forceinline__ void reg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
@@ -221,15 +241,20 @@ __host__ __device__ constexpr uint32_t make_idesc(int bn) {
 template <int BN> struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = (BN == 256) ? 3 : 5;
   static constexpr int TMEM_BUFS = TMEM_COLS / BN;
   static constexpr int SEG = BN / 4;  // columns per thread segment (two segments per thread)
-  // dynamic smem: stages | barriers (full, empty, tmem_full, tmem_empty) | misc
-  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 2 * TMEM_BUFS + 2;
+  // Staging tile of the epilogue: BM rows of BN 16-bit values.  Rows are padded by 16 bytes so
+  // that the 16-byte stores of 32 threads holding 32 different rows spread over all banks.
+  static constexpr int STAGING_ROW_BYTES = BN * 2 + 16;
+  static constexpr int STAGING_BYTES = BM * STAGING_ROW_BYTES;
+  // dynamic smem: stages | staging tile | barriers (full, empty, tmem_full, tmem_empty, drain,
+  // staged, staging_free) | misc
+  static constexpr int STAGING_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = STAGING_OFF + STAGING_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 2 * TMEM_BUFS + 3;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
-  static constexpr int XCHG_OFF = (MISC_OFF + 16 + 15) / 16 * 16;  // 2 tiles x 2 warpgroups x 128 floats
-  static constexpr int SMEM_BYTES = XCHG_OFF + 4 * BM * 4 + 1024;  // + slack for 1024 B alignment
+  static constexpr int SMEM_BYTES = MISC_OFF + 16 + 1024;  // + slack for 1024 B alignment
 };
 
 struct Tile {
@@ -309,10 +334,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + C::TMEM_BUFS + b); };
   const uint32_t drain_bar = bar_base + 8u * (2 * C::STAGES + 2 * C::TMEM_BUFS);
-  const uint32_t xchg_bar = drain_bar + 8u;
+  const uint32_t staged_bar = drain_bar + 8u;   // promotion warps -> epilogue warps: tile is in the staging buffer
+  const uint32_t sfree_bar = drain_bar + 16u;   // epilogue warps -> promotion warps: staging buffer may be reused
+  uint8_t* staging = smem + C::STAGING_OFF;
+  constexpr bool STAGED = sizeof(OutT) == 2;
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + C::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::MISC_OFF + 4);
-  float* xchg = reinterpret_cast<float*>(smem + C::XCHG_OFF);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -331,7 +358,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       mbar_init(tempty_bar(b), EPI_WARPS);
     }
     mbar_init(drain_bar, 1);
-    mbar_init(xchg_bar, EPI_WARPS * 32);
+    mbar_init(staged_bar, EPI_WARPS);
+    mbar_init(sfree_bar, STORE_WARPS);
     abort_flag[0] = 0;
     abort_flag[1] = 0;   // private flag of the drain waits
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -432,6 +460,88 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         mbar_wait(drain_bar, 0, abort_flag + 1, 40000000ull);
       }
     }
+  } else if (STAGED) {
+    // ---- epilogue warps: empty the staging tile while the next tile is being computed ----
+    const int ew = warp - STORE_WARP0;
+    uint32_t tile_no = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
+      const Tile ti = decode_tile<BN, MODE>(g, t);
+      if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
+        // A staging row holds the tile's 128 gate columns, then its 128 up columns, already
+        // rounded to OutT.  Reference rounding points: silu(gate)*up -> OutT, then
+        // scale = absmax * (1/448), q = h / scale (dlblas/kernels/moe.py:398-417), or the
+        // max(absmax, eps) / 448 form of dlblas/kernels/fp8.py:9-182.  Same arithmetic as
+        // silu_mul_quant_kernel, bit for bit.
+        if (!mbar_wait(staged_bar, tile_no & 1u, abort_flag, limit)) {
+          ok = false;
+          break;
+        }
+        const long long groups = g.n_half / 128;
+        // half a warp per row, eight columns per lane: two rows per pass, eight independent
+        // chains per lane to cover the exp / divide latencies
+        const int sub = lane >> 4;
+        const int cl = lane & 15;
+        for (int row0 = ew * 2; row0 < ti.rows; row0 += 2 * STORE_WARPS) {
+          const int row = row0 + sub;
+          const bool act = row < ti.rows;
+          const uint8_t* srow = staging + (act ? row : row0) * C::STAGING_ROW_BYTES;
+          const uint4 gv = *reinterpret_cast<const uint4*>(srow + cl * 16);
+          const uint4 uv = *reinterpret_cast<const uint4*>(srow + BN + cl * 16);
+          const OutT* gp = reinterpret_cast<const OutT*>(&gv);
+          const OutT* up = reinterpret_cast<const OutT*>(&uv);
+          float h[8];
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float gt = to_f32<OutT>(gp[j]);
+            h[j] = to_f32<OutT>(from_f32<OutT>(silu_fast(gt) * to_f32<OutT>(up[j])));
+            amax = fmaxf(amax, fabsf(h[j]));
+          }
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          const float scale =
+              g.quant_mode == DLB_QUANT_RECIP_MUL ? amax * (1.0f / 448.0f) : fmaxf(amax, g.quant_eps) / 448.0f;
+          if (act) {
+            const long long p = (long long)ti.row0 + row;
+            const uint2 q = quant8_rcp(h, 1.0f / scale);
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(g.c) + p * g.ldc + ti.n0 + cl * 8) = q;
+            if (cl == 0) g.q_scale[p * groups + ti.n0 / 128] = scale;
+          }
+        }
+      } else {
+        // this lane sends rows ew*64 + lane and ew*64 + 32 + lane
+        long long crow[2];
+        bool valid[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int row = ew * 64 + i * 32 + lane;
+          valid[i] = row < ti.rows;
+          crow[i] = (long long)ti.row0 + row;
+          if constexpr (MODE == DLB_EPI_SCATTER_WEIGHT) {
+            if (valid[i]) crow[i] = g.sorted_idx[crow[i]];
+          }
+        }
+        if (!mbar_wait(staged_bar, tile_no & 1u, abort_flag, limit)) {
+          ok = false;
+          break;
+        }
+        const uint32_t bytes = (uint32_t)min(BN, g.n - ti.n0) * 2u;   // n % 8 == 0
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (valid[i]) {
+            const int row = ew * 64 + i * 32 + lane;
+            bulk_store(reinterpret_cast<OutT*>(g.c) + crow[i] * g.ldc + ti.n0,
+                       smem_u32(staging + row * C::STAGING_ROW_BYTES), bytes);
+          }
+        }
+        bulk_commit();
+        bulk_wait_read();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sfree_bar);
+    }
+    bulk_wait_all();
   }
   } else {
     // ---- promotion + epilogue warps ------------------------------------------
@@ -582,56 +692,41 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       }
       if (!ok) break;
 
-      // ---- epilogue ---------------------------------------------------------
+      // ---- hand the tile over ------------------------------------------------
       float acc[2 * SEG];
 #pragma unroll
       for (int j = 0; j < SEG; ++j) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
-      if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
-        // reference rounding points: GEMM1 output -> OutT, silu(gate)*up -> OutT, then
-        // scale = absmax * (1/448), q = h / scale (dlblas/kernels/moe.py:398-417).
-        float h[SEG];
-        float amax = 0.f;
+      if constexpr (MODE == DLB_EPI_SCATTER_WEIGHT) {
 #pragma unroll
-        for (int j = 0; j < SEG; ++j) {
-          const float gt = to_f32<OutT>(from_f32<OutT>(acc[j]));
-          const float up = to_f32<OutT>(from_f32<OutT>(acc[SEG + j]));
-          const float sv = gt / (1.f + __expf(-gt));
-          h[j] = to_f32<OutT>(from_f32<OutT>(sv * up));
-          amax = fmaxf(amax, fabsf(h[j]));
-        }
-        // the two warpgroups hold the two halves of each row's 128-wide quantisation group:
-        // exchange the partial maxima through smem (double-buffered by tile parity, one
-        // bounded barrier phase per tile)
-        float* xb = xchg + (tile_no & 1u) * 2 * BM;
-        xb[wg * BM + r] = amax;
-        mbar_arrive(xchg_bar);
-        if (!mbar_wait(xchg_bar, tile_no & 1u, abort_flag, limit)) {
+        for (int j = 0; j < 2 * SEG; ++j) acc[j] *= row_w;
+      }
+      if constexpr (STAGED) {
+        // the staging tile must have been emptied by the epilogue warps (previous tile)
+        if (!mbar_wait(sfree_bar, (tile_no & 1u) ^ 1u, abort_flag, limit)) {
           ok = false;
           break;
         }
-        amax = fmaxf(amax, xb[(wg ^ 1) * BM + r]);
-        const float scale = g.quant_mode == DLB_QUANT_RECIP_MUL ? amax * (1.0f / 448.0f) : fmaxf(amax, g.quant_eps) / 448.0f;
-        if (row_ok) {
-          uint8_t* dst = reinterpret_cast<uint8_t*>(g.c) + p * g.ldc + ti.n0 + wg * SEG;
+        uint8_t* srow = staging + r * C::STAGING_ROW_BYTES;
+        // byte offsets of this thread's two segments inside the staging row; the fused w13
+        // epilogue wants all gate columns first, then all up columns
+        const int off0 = (MODE == DLB_EPI_SWIGLU_QUANT) ? wg * SEG * 2 : seg_col[0] * 2;
+        const int off1 = (MODE == DLB_EPI_SWIGLU_QUANT) ? BN + wg * SEG * 2 : seg_col[1] * 2;
 #pragma unroll
-          for (int j = 0; j < SEG; j += 16) {
-            uint32_t w[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint16_t lo = f32x2_to_e4m3x2(h[j + 4 * q] / scale, h[j + 4 * q + 1] / scale);
-              const uint16_t hi = f32x2_to_e4m3x2(h[j + 4 * q + 2] / scale, h[j + 4 * q + 3] / scale);
-              w[q] = (uint32_t)lo | ((uint32_t)hi << 16);
-            }
-            *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-          if (wg == 0) g.q_scale[p * (long long)(g.n_half / 128) + ti.n0 / 128] = scale;
+        for (int j = 0; j < 2 * SEG; j += 8) {
+          uint4 v;
+          v.x = Pack<OutT>::two(acc[j], acc[j + 1]);
+          v.y = Pack<OutT>::two(acc[j + 2], acc[j + 3]);
+          v.z = Pack<OutT>::two(acc[j + 4], acc[j + 5]);
+          v.w = Pack<OutT>::two(acc[j + 6], acc[j + 7]);
+          const int off = (j < SEG) ? off0 + j * 2 : off1 + (j - SEG) * 2;
+          *reinterpret_cast<uint4*>(srow + off) = v;
         }
+        // the rows leave through the async proxy (bulk copies): order these writes before it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(staged_bar);
       } else {
         if (row_ok) {
-          if constexpr (MODE == DLB_EPI_SCATTER_WEIGHT) {
-#pragma unroll
-            for (int j = 0; j < 2 * SEG; ++j) acc[j] *= row_w;
-          }
           const int col0 = ti.n0 + seg_col[0];
           OutT* dst = reinterpret_cast<OutT*>(g.c) + crow * g.ldc + col0;
           const int ncols = min(2 * SEG, g.n - col0);   // n % 8 == 0

@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(THREADS) silu_mul_quant_kernel(const T* __rest
       Vec8<T>::load(in + row * 2 * n + n + c, up);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        float s = g[i] / (1.f + __expf(-g[i]));
+        float s = silu_fast(g[i]);
         if (round_silu) s = to_f32<T>(from_f32<T>(s));
         h[i] = to_f32<T>(from_f32<T>(s * up[i]));
       }
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(THREADS) silu_mul_quant_kernel(const T* __rest
     amax = group_max(amax, 16);
     const float scale = quant_scale(amax, mode, eps);
     if (!active) continue;
-    *reinterpret_cast<uint2*>(q + row * n + c) = quant8(h, scale);
+    *reinterpret_cast<uint2*>(q + row * n + c) = quant8_rcp(h, 1.0f / scale);
     if (((c / 8) & 15) == 0) scales[row * groups + c / 128] = scale;
   }
 }
