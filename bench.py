@@ -252,12 +252,14 @@ class Layer:
         return routed.add_(shared)
 
 
-def time_steps(fn, steps, dev):
+def time_steps(fn, steps, dev, before_end=None):
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(dev)
     start.record()
     for _ in range(steps):
         fn()
+    if before_end is not None:
+        before_end()                 # e.g. make the timing stream wait for side streams
     end.record()
     torch.cuda.synchronize(dev)
     return start.elapsed_time(end)
@@ -291,11 +293,46 @@ def run_b200(args):
     def step_resident():
         return layer.step(x_d, logits_d, bias_d)
 
+    # End-to-end step: every step copies its inputs from pinned host memory and its result back.
+    # The copies run on their own streams over double-buffered device inputs, so the upload of
+    # step i + 1 and the download of step i - 1 overlap the kernels of step i (PCIe is full duplex).
+    h2d_stream, d2h_stream = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    in_bufs = [(torch.empty_like(x_d), torch.empty_like(logits_d)) for _ in range(2)]
+    out_pins = [out_pin, torch.empty_like(out_pin).pin_memory()]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    out_done = [torch.cuda.Event() for _ in range(2)]
+    e2e_state = {"i": 0}
+
     def step_e2e():
-        x_d.copy_(x_pin, non_blocking=True)
-        logits_d.copy_(logits_pin, non_blocking=True)
-        out = layer.step(x_d, logits_d, bias_d)
-        out_pin.copy_(out, non_blocking=True)
+        i = e2e_state["i"]
+        e2e_state["i"] = i + 1
+        b = i & 1
+        cur = torch.cuda.current_stream(dev)
+        xb, lb = in_bufs[b]
+        with torch.cuda.stream(h2d_stream):
+            if i >= 2:
+                h2d_stream.wait_event(in_free[b])         # step i - 2 has consumed this buffer
+            xb.copy_(x_pin, non_blocking=True)
+            lb.copy_(logits_pin, non_blocking=True)
+            in_ready[b].record(h2d_stream)
+        cur.wait_event(in_ready[b])
+        out = layer.step(xb, lb, bias_d)
+        in_free[b].record(cur)
+        done = torch.cuda.Event()
+        done.record(cur)
+        with torch.cuda.stream(d2h_stream):
+            d2h_stream.wait_event(done)
+            if i >= 2:
+                d2h_stream.wait_event(out_done[b])        # keep the pinned buffer's copies in order
+            out_pins[b].copy_(out, non_blocking=True)
+            out.record_stream(d2h_stream)
+            out_done[b].record(d2h_stream)
+
+    def drain_e2e():
+        cur = torch.cuda.current_stream(dev)
+        cur.wait_stream(d2h_stream)
+        cur.wait_stream(h2d_stream)
 
     for _ in range(max(args.warmup, 3)):
         step_resident()
@@ -316,8 +353,9 @@ def run_b200(args):
     clocks = sampler.stop(wall0, wall1) if rank == 0 else None
     for _ in range(2):
         step_e2e()
+    drain_e2e()
     barrier()
-    ms_e2e = time_steps(step_e2e, args.steps, dev)
+    ms_e2e = time_steps(step_e2e, args.steps, dev, before_end=drain_e2e)
     barrier()
     _C.check_status(dev)
     if world > 1:
