@@ -54,9 +54,11 @@ SIGNATURES = {
                                    c_vp, c_vp, c_int, c_vp, c_vp, c_vp]),
     "dlb_p2p_unpack_meta": (c_int, [c_vp, c_int, c_int, c_vp, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
     "dlb_p2p_push_rows": (c_int, [c_vp, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
+    "dlb_eplb_map_hash": (c_int, [c_vp, c_int, c_vp, c_vp, c_i64, c_int, c_int, c_int, ctypes.c_uint32, c_vp, c_vp]),
     "dlb_route_softmax_topk": (c_int, [c_vp, c_int, c_i64, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp]),
     "dlb_route_grouped_topk": (c_int, [c_vp, c_int, c_vp, c_i64, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp]),
     "dlb_topk_gating_workspace_size": (c_sz, [c_i64, c_int, c_int]),
+    "dlb_topk_gating_bwd": (c_int, [c_vp, c_sz, c_int, c_i64, c_int, c_int, c_i64, c_vp, c_vp, c_vp, c_vp]),
     "dlb_topk_gating": (c_int, [c_vp, c_int, c_i64, c_int, c_int, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
 }
 

@@ -220,7 +220,8 @@ __global__ void __launch_bounds__(WARPS * 32) gating_part1_kernel(const T* __res
 // (topk_gating_fwd_part2.py:31-36); fixed summation order, no atomics.
 __global__ void __launch_bounds__(256) gating_colsum_kernel(const float* __restrict__ gates,
                                                             const int* __restrict__ ids_km, long long tokens,
-                                                            int experts, float* __restrict__ res) {
+                                                            int experts, float* __restrict__ res,
+                                                            float* __restrict__ ce_out) {
   __shared__ float s_sum[8][33];
   __shared__ int s_cnt[8][33];
   const int ex = threadIdx.x & 31, y = threadIdx.x >> 5;
@@ -246,6 +247,7 @@ __global__ void __launch_bounds__(256) gating_colsum_kernel(const float* __restr
     const float me = tot / (float)tokens;
     const float ce = (float)c / (float)tokens;
     res[e] = me * ce * (float)experts * (float)experts;
+    ce_out[e] = ce;                                     // kept for the backward pass
   }
 }
 
@@ -399,10 +401,71 @@ template <int VPT> struct GatingLauncher {
   }
 };
 
+// Backward of the gating: d(l_aux)/d(logits) and, on request, d(token_exp_weights)/d(logits).
+//   add[e]  = ce[e] * grad_l_aux * E / T                                  (dlblas/kernels/topk_gating_bwd.py:31-33)
+//           + sum over kept slots j with ids[j] == e of
+//             ( gw[j] / D + [D not clamped] * sum_i(-gw[i] * g[i] / D^2) )   (w[j] = g[j] / D, D = sum of kept gates)
+//   grad[e] = gates[e] * (add[e] - sum_i gates[i] * add[i])                (softmax backward, :40-44)
+// One warp per token; reads what the forward left in its workspace.
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32) gating_bwd_kernel(const float* __restrict__ gates,
+                                                                const float* __restrict__ ce,
+                                                                const int* __restrict__ ids_km,
+                                                                const float* __restrict__ gate_km,
+                                                                const int* __restrict__ rank, long long tokens,
+                                                                int experts, int top_k, long long capacity,
+                                                                const T* __restrict__ grad_l_aux,
+                                                                const T* __restrict__ grad_w, T* __restrict__ grad_logits) {
+  const int lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * WARPS + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const float gl = to_f32<T>(*grad_l_aux) * (float)experts / (float)tokens;
+  const float eps = sizeof(T) == 2 ? 9.765625e-4f : 1.1920929e-7f;   // torch.finfo(dtype).eps
+  float denom = 0.f, coupling = 0.f;
+  if (grad_w != nullptr) {
+    for (int j = 0; j < top_k; ++j) {
+      const long long f = (long long)j * tokens + t;
+      if (rank[f] < capacity) denom += gate_km[f];
+    }
+    const bool clamped = denom < eps;
+    const float cd = clamped ? eps : denom;
+    if (!clamped) {
+      for (int j = 0; j < top_k; ++j) {
+        const long long f = (long long)j * tokens + t;
+        if (rank[f] < capacity) coupling -= to_f32<T>(grad_w[f]) * gate_km[f] / (cd * cd);
+      }
+    }
+    denom = cd;
+  }
+  const float* g_row = gates + t * experts;
+  float dot = 0.f;
+  for (int e = lane; e < experts; e += 32) {
+    float add = ce[e] * gl;
+    if (grad_w != nullptr) {
+      for (int j = 0; j < top_k; ++j) {
+        const long long f = (long long)j * tokens + t;
+        if (ids_km[f] == e && rank[f] < capacity) add += to_f32<T>(grad_w[f]) / denom + coupling;
+      }
+    }
+    dot += g_row[e] * add;
+  }
+  dot = warp_sum(dot);
+  for (int e = lane; e < experts; e += 32) {
+    float add = ce[e] * gl;
+    if (grad_w != nullptr) {
+      for (int j = 0; j < top_k; ++j) {
+        const long long f = (long long)j * tokens + t;
+        if (ids_km[f] == e && rank[f] < capacity) add += to_f32<T>(grad_w[f]) / denom + coupling;
+      }
+    }
+    grad_logits[t * experts + e] = from_f32<T>(g_row[e] * (add - dot));
+  }
+}
+
 size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 struct GatingWs {
-  size_t gates, ids_km, gate_km, rank, res, counts, sort, bytes;
+  size_t gates, ids_km, gate_km, rank, res, ce, counts, sort, bytes;
 };
 GatingWs gating_ws(long long tokens, int experts, int top_k) {
   GatingWs w;
@@ -412,16 +475,74 @@ GatingWs gating_ws(long long tokens, int experts, int top_k) {
   w.gate_km = off; off += align256((size_t)tokens * top_k * 4);
   w.rank = off; off += align256((size_t)tokens * top_k * 4);
   w.res = off; off += align256((size_t)experts * 4);
+  w.ce = off; off += align256((size_t)experts * 4);
   w.counts = off; off += align256((size_t)experts * 4);
   w.sort = off; off += sort_workspace_size(tokens * top_k, experts);
   w.bytes = off;
   return w;
 }
 
+// Logical -> physical expert ids for replicated experts: slot (t, k) of a token picks replica
+// hash32((t << 16) ^ (k << 8) ^ seed) & 0x7fffffff mod logcnt[e] of its logical expert e
+// (dlblas/kernels/moe.py:524-556; all arithmetic in 32 bits, as in the golden model of
+// tests/kernels/test_eplb.py:60-90).  Negative ids and experts without a replica give -1.
+constexpr int EPLB_THREADS = 256;
+template <typename IdT>
+__global__ void __launch_bounds__(EPLB_THREADS) eplb_map_hash_kernel(const IdT* __restrict__ topk_idx,
+                                                                const int* __restrict__ log2phy,
+                                                                const int* __restrict__ logcnt, long long slots,
+                                                                int top_k, int num_logical, int max_replica,
+                                                                uint32_t seed, int* __restrict__ out) {
+  for (long long i = (long long)blockIdx.x * EPLB_THREADS + threadIdx.x; i < slots; i += (long long)gridDim.x * EPLB_THREADS) {
+    const long long e = (long long)topk_idx[i];
+    int phy = -1;
+    if (e >= 0 && e < num_logical) {
+      const int cnt = __ldg(logcnt + e);
+      if (cnt > 0) {
+        const uint32_t t = (uint32_t)(i / top_k);
+        const uint32_t k = (uint32_t)(i - (long long)t * top_k);
+        uint32_t x = (t << 16) ^ (k << 8) ^ seed;
+        x = ((x >> 16) ^ x) * 0x45d9f3bu;
+        x = ((x >> 16) ^ x) * 0x45d9f3bu;
+        x = (x >> 16) ^ x;
+        const uint32_t replica = (x & 0x7fffffffu) % (uint32_t)cnt;
+        phy = __ldg(log2phy + e * max_replica + replica);
+      }
+    }
+    out[i] = phy;
+  }
+}
+
 }  // namespace
 }  // namespace dlb
 
 using namespace dlb;
+
+extern "C" int dlb_eplb_map_hash(const void* topk_idx, int ids_dtype, const int32_t* log2phy, const int32_t* logcnt,
+                                 int64_t tokens, int top_k, int num_logical, int max_replica, uint32_t seed,
+                                 int32_t* physical_idx, void* stream) {
+  DLB_REQUIRE(tokens >= 0 && top_k > 0 && num_logical > 0 && max_replica > 0, DLB_ERR_INVALID,
+              "eplb_map_hash: bad sizes tokens=%lld top_k=%d experts=%d replicas=%d", (long long)tokens, top_k,
+              num_logical, max_replica);
+  if (tokens == 0) return DLB_OK;
+  DLB_REQUIRE(topk_idx && log2phy && logcnt && physical_idx, DLB_ERR_INVALID, "eplb_map_hash: null pointer");
+  const long long slots = tokens * top_k;
+  const int grid = (int)std::min<long long>(ceil_div(slots, (long long)EPLB_THREADS), (long long)sm_count() * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (ids_dtype == DLB_I32) {
+    eplb_map_hash_kernel<int><<<grid, EPLB_THREADS, 0, st>>>(reinterpret_cast<const int*>(topk_idx), log2phy, logcnt, slots,
+                                                        top_k, num_logical, max_replica, seed, physical_idx);
+  } else if (ids_dtype == DLB_I64) {
+    eplb_map_hash_kernel<long long><<<grid, EPLB_THREADS, 0, st>>>(reinterpret_cast<const long long*>(topk_idx), log2phy,
+                                                              logcnt, slots, top_k, num_logical, max_replica, seed,
+                                                              physical_idx);
+  } else {
+    return fail(DLB_ERR_INVALID, "eplb_map_hash: ids must be int32 or int64 (got %d)", ids_dtype);
+  }
+  count_launch();
+  DLB_CHECK_LAUNCH("eplb_map_hash_kernel");
+  return DLB_OK;
+}
 
 extern "C" int dlb_route_softmax_topk(const void* logits, int dtype, int64_t tokens, int experts, int top_k,
                                       int renormalize, float* weights, void* ids, int ids_dtype, void* stream) {
@@ -488,7 +609,8 @@ extern "C" int dlb_topk_gating(const void* logits, int dtype, int64_t tokens, in
   GatingArgs a = {logits, dtype, tokens, experts, top_k, gates, ids_km, gate_km, st};
   int rc = dispatch_vpt<GatingLauncher>(experts, a);
   if (rc != DLB_OK) return rc;
-  gating_colsum_kernel<<<(int)ceil_div(experts, 32), 256, 0, st>>>(gates, ids_km, tokens, experts, res);
+  gating_colsum_kernel<<<(int)ceil_div(experts, 32), 256, 0, st>>>(gates, ids_km, tokens, experts, res,
+                                                                   reinterpret_cast<float*>(ws + w.ce));
   count_launch();
   DLB_CHECK_LAUNCH("gating_colsum_kernel");
   // position of every (slot, token) entry inside its expert, in k-major / token-minor order:
@@ -513,5 +635,38 @@ extern "C" int dlb_topk_gating(const void* logits, int dtype, int64_t tokens, in
                                                                           capacity, reinterpret_cast<long long*>(select));
   count_launch();
   DLB_CHECK_LAUNCH("gating_fill_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_topk_gating_bwd(const void* workspace, size_t workspace_bytes, int dtype, int64_t tokens, int experts,
+                                   int top_k, int64_t capacity, const void* grad_l_aux, const void* grad_weights,
+                                   void* grad_logits, void* stream) {
+  DLB_REQUIRE(tokens > 0 && experts > 0 && experts <= 32 * MAX_VPT && top_k > 0 && top_k <= experts, DLB_ERR_INVALID,
+              "topk_gating_bwd: bad sizes tokens=%lld experts=%d top_k=%d", (long long)tokens, experts, top_k);
+  DLB_REQUIRE(dtype == DLB_F32 || dtype == DLB_F16, DLB_ERR_INVALID, "topk_gating_bwd: dtype must be fp32 or fp16");
+  DLB_REQUIRE(workspace && grad_l_aux && grad_logits, DLB_ERR_INVALID, "topk_gating_bwd: null pointer");
+  const GatingWs w = gating_ws(tokens, experts, top_k);
+  DLB_REQUIRE(workspace_bytes >= w.bytes, DLB_ERR_WORKSPACE,
+              "topk_gating_bwd: the forward's workspace has %zu bytes, %zu given", w.bytes, workspace_bytes);
+  const char* ws = reinterpret_cast<const char*>(workspace);
+  const float* gates = reinterpret_cast<const float*>(ws + w.gates);
+  const float* ce = reinterpret_cast<const float*>(ws + w.ce);
+  const int* ids_km = reinterpret_cast<const int*>(ws + w.ids_km);
+  const float* gate_km = reinterpret_cast<const float*>(ws + w.gate_km);
+  const int* rank = reinterpret_cast<const int*>(ws + w.rank);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = (int)ceil_div(tokens, WARPS);
+  if (dtype == DLB_F32)
+    gating_bwd_kernel<float><<<grid, WARPS * 32, 0, st>>>(gates, ce, ids_km, gate_km, rank, tokens, experts, top_k,
+                                                          capacity, reinterpret_cast<const float*>(grad_l_aux),
+                                                          reinterpret_cast<const float*>(grad_weights),
+                                                          reinterpret_cast<float*>(grad_logits));
+  else
+    gating_bwd_kernel<__half><<<grid, WARPS * 32, 0, st>>>(gates, ce, ids_km, gate_km, rank, tokens, experts, top_k,
+                                                           capacity, reinterpret_cast<const __half*>(grad_l_aux),
+                                                           reinterpret_cast<const __half*>(grad_weights),
+                                                           reinterpret_cast<__half*>(grad_logits));
+  count_launch();
+  DLB_CHECK_LAUNCH("gating_bwd_kernel");
   return DLB_OK;
 }

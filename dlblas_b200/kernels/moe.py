@@ -50,3 +50,11 @@ def biased_grouped_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor
     assert n_share_experts_fusion == 0, "n_share_experts_fusion is not supported"
     return ops.route_grouped_topk(gating_output.contiguous(), correction_bias, topk, renormalize, num_expert_group,
                                   topk_group)
+
+
+def map_logic_to_physical_idx_hash_random(topk_idx: torch.Tensor, log2phy: torch.Tensor, logcnt: torch.Tensor,
+                                          seed: int = 12345, block_size: int = 128) -> torch.Tensor:
+    """Logical -> physical expert ids for replicated experts (:558-579 of the reference): slot (t, k) goes to
+    replica hash32((t << 16) ^ (k << 8) ^ seed) mod logcnt[e]; -1 for negative ids / experts without replicas.
+    `block_size` is the reference's launch parameter and has no effect here."""
+    return ops.eplb_map_hash(topk_idx, log2phy, logcnt, seed)

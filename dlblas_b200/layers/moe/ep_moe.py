@@ -15,6 +15,7 @@ from ...kernels.fused_moe_v3 import fused_moe_v3
 from ...kernels.moe import silu_and_mul_masked_post_quant_fwd
 from ...utils.logger import get_logger
 from ...utils.utils import DisposibleTensor
+from .experts_distribution_recorder import ExpertsDistributionRecorder
 from .kernels.blocked_fp8_fused_moe import _renormalize, moe_expert_forward
 from .token_dispatcher import TokenDispatcherLowLatency, TokenDispatcherNormal, TokenDispatcherP2P
 
@@ -26,6 +27,7 @@ enable_moe_load_stats = os.environ.get("DLBLAS_MOE_LOAD_STATS", "false").lower()
 class FusedMoENormal:
     """Expert-parallel prefill layer: quantise, dispatch to the ranks that own the routed experts,
     run the experts on the received tokens, combine back (ep_moe.py:34-152)."""
+    recorder = ExpertsDistributionRecorder(output_dir="/tmp/dlblas/prefill_moe_stats")
 
     def __init__(self, ep_size: int, ep_group: dist.ProcessGroup, num_experts: int, hidden_dim: int,
                  layer_index: int = 0, block_size: int = 128, top_k: int = 8,
@@ -52,6 +54,8 @@ class FusedMoENormal:
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,
                 up_weights: torch.Tensor, up_scale: torch.Tensor, down_weights: torch.Tensor,
                 down_scale: torch.Tensor, expert_list: List[int] = None):
+        if enable_moe_load_stats:
+            FusedMoENormal.recorder.record(topk_ids, self.layer_index, self.num_experts)
         if self.p2p_dispatcher is not None:
             d = self.p2p_dispatcher
             hs = hidden_states.flatten(0, -2) if hidden_states.dim() > 2 else hidden_states
@@ -103,6 +107,7 @@ class FusedMoELowLatency:
     """Expert-parallel decode layer on the masked layout [E_local, max_tokens * world, H]
     (ep_moe.py:155-347): dispatch casts to FP8, the experts run two masked grouped GEMMs with the fused
     silu*up + quantisation between them, combine applies the routing weights."""
+    recorder = ExpertsDistributionRecorder(output_dir="/tmp/dlblas/decode_moe_stats")
 
     def __init__(self, ep_size: int, ep_group: dist.ProcessGroup, num_experts: int, hidden_dim: int,
                  layer_index: int, block_size: int = 128, out_dtype: torch.dtype = torch.bfloat16):
@@ -145,6 +150,8 @@ class FusedMoELowLatency:
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,
                 up_weights: torch.Tensor, up_scale: torch.Tensor, down_weights: torch.Tensor,
                 down_scale: torch.Tensor, expert_list: List[int] = None):
+        if enable_moe_load_stats:
+            FusedMoELowLatency.recorder.record(topk_ids, self.layer_index, self.num_experts)
         recv_hidden_states, topk_idx, topk_weights, masked_m, expected_m = self.token_dispatcher.dispatch(
             hidden_states, topk_ids, topk_weights, self.num_experts)
         out_states = self.experts(recv_hidden_states, up_weights, up_scale, down_weights, down_scale, masked_m,

@@ -222,6 +222,22 @@ def ep_scatter(x, x_scale, ids, counts, expert_start_loc, out_x, out_scale, m_in
 
 
 # --------------------------------------------------------------------------- routing
+def eplb_map_hash(topk_idx: torch.Tensor, log2phy: torch.Tensor, logcnt: torch.Tensor, seed: int = 12345):
+    """Hash choice of a physical replica per (token, slot); int32 [tokens, top_k]."""
+    require_cuda(topk_idx, log2phy, logcnt)
+    assert topk_idx.dim() == 2 and log2phy.dim() == 2 and logcnt.numel() == log2phy.shape[0]
+    assert topk_idx.dtype in (torch.int32, torch.int64)
+    topk_idx = topk_idx.contiguous()
+    log2phy = log2phy.to(torch.int32).contiguous()
+    logcnt = logcnt.to(torch.int32).contiguous()
+    t, k = topk_idx.shape
+    out = torch.empty(t, k, dtype=torch.int32, device=topk_idx.device)
+    check(lib().dlb_eplb_map_hash(ptr(topk_idx), dtype_code(topk_idx.dtype), ptr(log2phy), ptr(logcnt), t, k,
+                                  log2phy.shape[0], log2phy.shape[1], int(seed) & 0xFFFFFFFF, ptr(out),
+                                  stream(topk_idx.device)))
+    return out
+
+
 def route_softmax_topk(logits: torch.Tensor, top_k: int, renormalize: bool = False, ids_dtype=torch.int64):
     require_cuda(logits)
     assert logits.dim() == 2 and logits.is_contiguous()
@@ -247,7 +263,20 @@ def route_grouped_topk(logits: torch.Tensor, bias: torch.Tensor, top_k: int, ren
     return w, ids
 
 
-def topk_gating(logits: torch.Tensor, k: int, capacity: int):
+def topk_gating_bwd(ws: torch.Tensor, dtype, tokens: int, experts: int, k: int, capacity: int, grad_l_aux: torch.Tensor,
+                    grad_weights):
+    """grad of (l_aux, token_exp_weights) w.r.t. the logits from the forward's workspace `ws`."""
+    require_cuda(ws, grad_l_aux)
+    dev = ws.device
+    grad_l_aux = grad_l_aux.to(dtype).contiguous()
+    gw = None if grad_weights is None else grad_weights.to(dtype).contiguous()
+    out = torch.empty(tokens, experts, dtype=dtype, device=dev)
+    check(lib().dlb_topk_gating_bwd(ptr(ws), ws.numel(), dtype_code(dtype), tokens, experts, k, capacity,
+                                    ptr(grad_l_aux), 0 if gw is None else ptr(gw), ptr(out), stream(dev)))
+    return out
+
+
+def topk_gating(logits: torch.Tensor, k: int, capacity: int, return_workspace: bool = False):
     require_cuda(logits)
     assert logits.dim() == 2 and logits.is_contiguous()
     t, e = logits.shape
@@ -260,6 +289,8 @@ def topk_gating(logits: torch.Tensor, k: int, capacity: int):
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
     check(lib().dlb_topk_gating(ptr(logits), dtype_code(logits.dtype), t, e, k, capacity, ptr(l_aux), ptr(ec_idx), ptr(w),
                                 ptr(sel), ptr(ws), ws_bytes, stream(dev)))
+    if return_workspace:
+        return l_aux, ec_idx, w, sel, ws
     return l_aux, ec_idx, w, sel
 
 

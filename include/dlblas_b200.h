@@ -216,6 +216,15 @@ DLB_API int dlb_p2p_unpack_meta(const int32_t* meta, int meta_ints, int top_k, c
 DLB_API int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32_t* counts, int world, int my_rank,
                       int64_t region_rows, const void* const* peer_dst, void* stream);
 
+/* ---- expert-parallel load balancing ------------------------------------------------
+ * map_logic_to_physical_idx_hash_random (dlblas/kernels/moe.py:524-579): every (token, slot) of topk_idx
+ * [tokens, top_k] (int32 or int64) is sent to one of the logcnt[e] physical replicas log2phy[e, 0..) of its
+ * logical expert e, chosen by a 32-bit hash of (token, slot, seed); -1 for negative ids and for experts
+ * without replicas.  physical_idx int32 [tokens, top_k]. */
+DLB_API int dlb_eplb_map_hash(const void* topk_idx, int ids_dtype, const int32_t* log2phy, const int32_t* logcnt,
+                      int64_t tokens, int top_k, int num_logical, int max_replica, uint32_t seed,
+                      int32_t* physical_idx, void* stream);
+
 /* ---- routing -------------------------------------------------------------------
  * topk(softmax(logits, fp32), k) with lowest-index tie-break, optional w / sum(w): the routing the
  * reference's callers run in torch (tests/kernels/test_fused_moe_v2.py:100-102) + _renormalize
@@ -235,6 +244,15 @@ DLB_API size_t dlb_topk_gating_workspace_size(int64_t tokens, int experts, int t
 DLB_API int dlb_topk_gating(const void* logits, int dtype, int64_t tokens, int experts, int top_k, int64_t capacity,
                     void* l_aux, int32_t* ec_idx, void* gate_weights, int64_t* select, void* workspace,
                     size_t workspace_bytes, void* stream);
+/* Backward of dlb_topk_gating (TopKGatingFunc.backward, dlblas/kernels/topk_gating.py:270-285;
+ * topk_gating_bwd.py:13-68): gradient of l_aux and, if grad_weights (logits dtype, [k*tokens]) is given, of
+ * token_exp_weights with respect to the logits.  `workspace` is the forward call's workspace, unmodified.
+ * The reference's own weight path (topk_gating.py:139-242) cannot be reached through autograd (it reads the
+ * gradient of the integer index output) and divides the saved weights by the denominator twice; this entry
+ * computes the true gradient.  grad_l_aux is a device scalar of the logits dtype. */
+DLB_API int dlb_topk_gating_bwd(const void* workspace, size_t workspace_bytes, int dtype, int64_t tokens, int experts,
+                        int top_k, int64_t capacity, const void* grad_l_aux, const void* grad_weights,
+                        void* grad_logits, void* stream);
 
 #ifdef __cplusplus
 }

@@ -410,3 +410,73 @@ def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
     a = a.to(torch.float64)
     b = b.to(torch.float64)
     return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def eplb_hash_map(topk_idx: torch.Tensor, log2phy: torch.Tensor, logcnt: torch.Tensor, seed: int = 12345) -> torch.Tensor:
+    """dlblas/kernels/moe.py:524-556 and the golden model tests/kernels/test_eplb.py:60-90: replica
+    hash32((t << 16) ^ (k << 8) ^ seed) & 0x7fffffff mod logcnt[e], all arithmetic modulo 2^32."""
+    import numpy as np
+    t, k = topk_idx.shape
+    ids = topk_idx.cpu().numpy().astype(np.int64)
+    l2p = log2phy.cpu().numpy().astype(np.int64)
+    cnt = logcnt.cpu().numpy().astype(np.int64)
+    tt = np.arange(t, dtype=np.uint64)[:, None]
+    kk = np.arange(k, dtype=np.uint64)[None, :]
+    mask = np.uint64(0xFFFFFFFF)
+    x = ((tt << np.uint64(16)) ^ (kk << np.uint64(8)) ^ np.uint64(seed & 0xFFFFFFFF)) & mask
+    for _ in range(2):
+        x = (((x >> np.uint64(16)) ^ x) * np.uint64(0x45d9f3b)) & mask
+    x = ((x >> np.uint64(16)) ^ x) & np.uint64(0x7FFFFFFF)
+    safe_ids = np.clip(ids, 0, len(cnt) - 1)
+    c = cnt[safe_ids]
+    ok = (ids >= 0) & (c > 0)
+    replica = (x.astype(np.int64) % np.maximum(c, 1))
+    out = np.where(ok, l2p[safe_ids, np.minimum(replica, l2p.shape[1] - 1)], -1)
+    return torch.from_numpy(out.astype(np.int32))
+
+
+def topk_gating_grad(logits: torch.Tensor, k: int, capacity_factor: float, min_capacity: int, grad_l_aux,
+                     grad_weights=None) -> torch.Tensor:
+    """Gradient of (l_aux, token_exp_weights) with respect to the logits by automatic differentiation of
+    `topk_gating` above (indices, masks and capacity drops are constants; clamp passes the gradient where
+    the denominator is not clamped).  With grad_weights=None this is the reference's default backward,
+    dlblas/kernels/topk_gating_bwd.py:13-68 (only the auxiliary loss is differentiated)."""
+    x = logits.detach().to(torch.float32).clone().requires_grad_(True)
+    l_aux, _, w, _ = topk_gating(x, k, capacity_factor, min_capacity)
+    loss = l_aux * torch.as_tensor(grad_l_aux, dtype=torch.float32)
+    if grad_weights is not None:
+        loss = loss + (w * grad_weights.to(torch.float32).reshape(-1)).sum()
+    loss.backward()
+    return x.grad
+
+
+def topk_gating_bwd_reference_hp(logits: torch.Tensor, k: int, capacity_factor: float, min_capacity: int, grad_l_aux,
+                                 grad_weights: torch.Tensor) -> torch.Tensor:
+    """The two kernels of the reference's higher-precision backward exactly as written
+    (dlblas/kernels/topk_gating.py:139-183): they divide the saved, already normalised weights by the
+    denominator twice, so the coupling term is 1/denominator too small compared with the true gradient."""
+    t, e = logits.shape
+    lg = logits.to(torch.float32)
+    ex = torch.exp(lg)
+    gates = ex / ex.sum(dim=1, keepdim=True)
+    capacity = max(int(math.ceil((t / e) * (capacity_factor * k))), int(min_capacity))
+    _, ids = _first_max_topk(gates, k)
+    ids_ks = ids.t().contiguous()
+    masks = torch.nn.functional.one_hot(ids_ks.reshape(-1), num_classes=e)
+    locations = (torch.cumsum(masks, dim=0) - 1).reshape(k, t, e)
+    masks = masks.reshape(k, t, e)
+    ce = masks[0].to(torch.float32).mean(dim=0)
+    masks = masks * (locations < capacity)
+    gate_s, indices_s = torch.max(gates[None] * masks.to(torch.float32), dim=2)
+    indices_s = torch.where(masks.sum(dim=2) > 0, indices_s, torch.zeros_like(indices_s))
+    eps = torch.finfo(torch.float32).eps
+    denom = gate_s.sum(dim=0)
+    cd = torch.clamp(denom, min=eps)
+    w = gate_s / cd
+    gw = grad_weights.to(torch.float32).reshape(k, t)
+    coupling = torch.where(denom >= eps, (-gw * (w / cd / cd)).sum(dim=0), torch.zeros_like(denom))
+    add_1 = gw / cd + coupling
+    scat = torch.zeros(k, t, e).scatter_(2, indices_s.unsqueeze(-1), add_1.unsqueeze(-1))
+    add_2 = (scat * masks).sum(dim=0) + ce * torch.as_tensor(grad_l_aux, dtype=torch.float32) * e / t
+    dx = gates * add_2
+    return dx - gates * dx.sum(dim=1, keepdim=True)

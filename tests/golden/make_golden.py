@@ -202,6 +202,45 @@ def gold_topk_gating(ref, out):
     print("topk_gating:", len(cases), "cases")
 
 
+def gold_topk_gating_bwd(ref, out):
+    """Gradient of the gating's auxiliary loss with respect to the logits: the reference's default backward
+    (dlblas/kernels/topk_gating.py:270-276 -> topk_gating_bwd.py:50-68), and the two kernels of its
+    higher-precision backward (topk_gating.py:186-242) fed with the gradient of the token weights."""
+    import dlblas.kernels.topk_gating_fwd_part1 as p1
+    import dlblas.kernels.topk_gating_fwd_part2 as p2
+    p1.tl_exp = _exp
+    p2.logits = types.SimpleNamespace(device="cpu")
+    from dlblas.kernels.topk_gating import TopKGatingFunc, topk_bwd_triton, topk_fwd_triton
+    from dlblas.kernels.topk_gating import _capacity
+    from dlblas.kernels.topk_gating_fwd_part1 import call as part1
+    from dlblas.kernels.topk_gating_fwd_part2 import call as part2
+    cases = []
+    g = torch.Generator().manual_seed(9)
+    for (t, e, k, cf) in [(64, 8, 2, 1.0), (96, 16, 4, 0.5)]:
+        logits = torch.randn(t, e, generator=g).requires_grad_(True)
+        l_aux, ec, w, sel = TopKGatingFunc.apply(logits, k, cf, 2, False)
+        gl = torch.tensor(0.7)
+        l_aux.backward(gl)
+        case = dict(logits=logits.detach().clone(), k=k, capacity_factor=cf, min_capacity=2, grad_l_aux=gl,
+                    grad_logits_default=logits.grad.clone())
+        # higher-precision pieces, called directly (the autograd wrapper of the reference indexes the wrong
+        # output gradient, so it cannot be driven through .backward())
+        capacity = _capacity(logits.detach(), torch.tensor(cf * k), torch.tensor(2)).item()
+        gates, masks = part1(logits.detach(), k)
+        locations, res, ce = part2(gates, masks, k)
+        ec2, w2, sel2, for_bwd = topk_fwd_triton(gates, masks, locations, capacity)
+        gw = torch.randn(k * t, generator=g)
+        try:
+            grad = topk_bwd_triton(gates, ce, masks, *for_bwd, gl, gw.view(k, t))
+            case.update(grad_weights=gw, grad_logits_hp_reference=grad.clone(), weights_hp=w2.clone(),
+                        gate_ks=for_bwd[0].clone(), denom=for_bwd[2].clone())
+        except Exception as exc:
+            case["hp_error"] = repr(exc)[:300]
+        cases.append(case)
+    torch.save(cases, os.path.join(out, "topk_gating_bwd.pt"))
+    print("topk_gating_bwd:", len(cases), "cases", [c.get("hp_error", "hp ok") for c in cases])
+
+
 def gold_scatter_gather(ref, out):
     from dlblas.kernels.fused_moe_v3 import ep_gather, ep_scatter
     g = torch.Generator().manual_seed(8)
@@ -231,6 +270,78 @@ def gold_scatter_gather(ref, out):
     print("scatter_gather: ok")
 
 
+def gold_eplb(ref, out):
+    """Expert-parallel load balancer: the hash replica choice (Triton kernel under the interpreter and the
+    reference test's own golden model) and the re-balancing tables of dlblas/layers/moe/eplb.py."""
+    import importlib.util
+    from dlblas.kernels.moe import map_logic_to_physical_idx_hash_random
+    spec = importlib.util.spec_from_file_location("ref_test_eplb", os.path.join(ref, "tests", "kernels", "test_eplb.py"))
+    tmod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(tmod)
+    golden_model = tmod.reference_map_logic_to_physical_idx_hash_random
+    cases = []
+    # the known-answer inputs of tests/kernels/test_eplb.py:94-103
+    topk = torch.tensor([[1, 2], [2, 2], [0, 1], [1, 3]], dtype=torch.int32)
+    log2phy = torch.tensor([[10, 11], [12, 13], [14, -1], [15, 16]], dtype=torch.int32)
+    logcnt = torch.tensor([2, 2, 1, 2], dtype=torch.int32)
+    cases.append(dict(name="reference_test", topk_idx=topk, log2phy=log2phy, logcnt=logcnt, seed=99999))
+    g = torch.Generator().manual_seed(21)
+    for (t, k, e, r, seed) in [(70, 8, 32, 3, 12345), (300, 4, 16, 4, 7), (66000, 2, 8, 2, 99999)]:
+        logcnt = torch.randint(0, r + 1, (e,), generator=g, dtype=torch.int32)
+        log2phy = torch.full((e, r), -1, dtype=torch.int32)
+        nxt = 0
+        for i in range(e):
+            for j in range(int(logcnt[i])):
+                log2phy[i, j] = nxt
+                nxt += 1
+        topk = torch.randint(-1, e, (t, k), generator=g, dtype=torch.int32)
+        cases.append(dict(name=f"random_{t}x{k}", topk_idx=topk, log2phy=log2phy, logcnt=logcnt, seed=seed))
+    for c in cases:
+        small = c["topk_idx"].shape[0] <= 300
+        name = c["name"]
+        if small:
+            try:
+                c["kernel_out"] = map_logic_to_physical_idx_hash_random(c["topk_idx"], c["log2phy"], c["logcnt"],
+                                                                        seed=c["seed"]).clone()
+            except Exception as exc:   # the interpreter rejects the kernel's 0xFFFFFFFF literal as an int32 scalar
+                c["kernel_out"] = None
+                c["kernel_error"] = repr(exc)[:200]
+            c["model_out"] = golden_model(c["topk_idx"], c["log2phy"], c["logcnt"], seed=c["seed"])
+        else:
+            # the interpreter needs minutes for 66000 tokens: only the rows whose (t << 16) leaves 32 bits
+            sel = torch.arange(65530, 65560)
+            full = golden_model(c["topk_idx"][:65560], c["log2phy"], c["logcnt"], seed=c["seed"])
+            c["rows"] = sel
+            c["model_out_rows"] = full[sel]
+            c["num_tokens"] = c["topk_idx"].shape[0]
+            c["topk_rows"] = c["topk_idx"][sel].clone()      # tests rebuild the batch: these rows, -1 elsewhere
+            del c["topk_idx"]
+        print("eplb hash", name, "kernel == model:",
+              bool(torch.equal(c["kernel_out"], c["model_out"])) if small and c["kernel_out"] is not None else "n/a")
+
+    # ---- re-balancing tables (host code; the reference calls .cuda() on an index tensor) ----
+    torch.Tensor.cuda = lambda self, *a, **k: self
+    import dlblas.layers.moe.eplb as E
+    tables = []
+    g = torch.Generator().manual_seed(22)
+    for (layers, experts, replicas, groups, nodes, gpus) in [(2, 16, 24, 4, 1, 4), (3, 32, 40, 8, 2, 8),
+                                                             (2, 16, 20, 3, 2, 4), (1, 256, 288, 8, 1, 8),
+                                                             (2, 8, 8, 4, 1, 4)]:
+        w = (torch.rand(layers, experts, generator=g) * 1000).float()
+        phy2log, log2phy, logcnt = E.rebalance_experts(w, replicas, groups, nodes, gpus)
+        disp = E.compute_logical_to_rank_dispatch_physical_map(log2phy, gpus, replicas, seed=42)
+        tables.append(dict(weight=w, num_replicas=replicas, num_groups=groups, num_nodes=nodes, num_gpus=gpus,
+                           phy2log=phy2log, log2phy=log2phy, logcnt=logcnt, dispatch=disp))
+    # the default statistic of EPLBMetadata.init (descending integers: ties between load / replica quotients)
+    w = torch.arange(64, dtype=torch.int32).flip(dims=(0,)).expand(2, -1)
+    phy2log, log2phy, logcnt = E.rebalance_experts(w, 64 + 16, 4, 1, 8)
+    tables.append(dict(weight=w.clone(), num_replicas=80, num_groups=4, num_nodes=1, num_gpus=8, phy2log=phy2log,
+                       log2phy=log2phy, logcnt=logcnt,
+                       dispatch=E.compute_logical_to_rank_dispatch_physical_map(log2phy, 8, 80, seed=42)))
+    torch.save(dict(hash=cases, tables=tables), os.path.join(out, "eplb.pt"))
+    print("eplb:", len(cases), "hash cases,", len(tables), "tables")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
@@ -239,7 +350,7 @@ def main():
     a = ap.parse_args()
     install_shim(a.reference)
     todo = [gold_sort, gold_quant, gold_gemm, gold_grouped, gold_activation, gold_grouped_topk,
-            gold_topk_gating, gold_scatter_gather]
+            gold_topk_gating, gold_topk_gating_bwd, gold_scatter_gather, gold_eplb]
     for fn in todo:
         if a.only and a.only not in fn.__name__:
             continue

@@ -352,3 +352,30 @@ def test_topk_gating_random(t, e, k, cf):
         assert torch.equal(ec, o_ec) and torch.equal(sel, o_sel)
         torch.testing.assert_close(w, o_w, rtol=1e-5, atol=1e-7)
     torch.testing.assert_close(l_aux, o_l, rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("higher_precision", [False, True])
+def test_topk_gating_backward(golden, higher_precision):
+    import dlblas_b200
+    for c in golden("topk_gating_bwd.pt"):
+        logits = c["logits"].to(DEV).requires_grad_(True)
+        l_aux, ec, w, sel = dlblas_b200.topk_gating(logits, c["k"], c["capacity_factor"], c["min_capacity"],
+                                                    higher_precision)
+        gw = c["grad_weights"].to(DEV)
+        (l_aux * 0.7 + (w * gw).sum()).backward()
+        ref = O.topk_gating_grad(c["logits"], c["k"], c["capacity_factor"], c["min_capacity"], c["grad_l_aux"],
+                                 c["grad_weights"] if higher_precision else None)
+        torch.testing.assert_close(logits.grad.cpu(), ref, rtol=2e-4, atol=1e-6)
+        if not higher_precision:
+            torch.testing.assert_close(logits.grad.cpu(), c["grad_logits_default"], rtol=2e-4, atol=1e-6)
+    # fp16 logits, larger case
+    g = torch.Generator().manual_seed(5)
+    lg = torch.randn(300, 64, generator=g)
+    x = lg.half().to(DEV).requires_grad_(True)
+    l_aux, ec, w, sel = dlblas_b200.topk_gating(x, 4, 1.0, 2, higher_precision)
+    gw = torch.randn(4 * 300, generator=g)
+    (l_aux.float() * 0.7 + (w.float() * gw.to(DEV)).sum()).backward()
+    ref = O.topk_gating_grad(lg.half().float(), 4, 1.0, 2, 0.7, gw.half().float() if higher_precision else None)
+    assert x.grad.dtype == torch.float16
+    tol = 2e-2 * float(ref.abs().max()) + 1e-6
+    assert float((x.grad.cpu().float() - ref).abs().max()) <= tol

@@ -142,3 +142,28 @@ def test_layer_tiny_config_self_consistency():
         parts.append(O.moe_layer(x, w, lid, w13[4 * r:4 * r + 4], w13s[4 * r:4 * r + 4], w2[4 * r:4 * r + 4],
                                  w2s[4 * r:4 * r + 4], top_k=2, expert_offset=4 * r, num_experts=8).float())
     assert O.rel_frobenius(parts[0] + parts[1], out.float()) < 1e-2
+
+
+def test_topk_gating_gradient_against_reference_backward(golden):
+    """The oracle's autograd gradient equals the reference's default backward (auxiliary loss only), and a
+    restatement of the reference's higher-precision kernels reproduces what they compute (which is not the
+    true gradient: the coupling term carries an extra 1 / denominator)."""
+    cases = golden("topk_gating_bwd.pt")
+    assert len(cases) == 2
+    for c in cases:
+        args = (c["logits"], c["k"], c["capacity_factor"], c["min_capacity"], c["grad_l_aux"])
+        g = O.topk_gating_grad(*args)
+        torch.testing.assert_close(g, c["grad_logits_default"], rtol=1e-5, atol=1e-9)
+        r = O.topk_gating_bwd_reference_hp(*args, c["grad_weights"])
+        torch.testing.assert_close(r, c["grad_logits_hp_reference"], rtol=1e-4, atol=1e-5)
+        true = O.topk_gating_grad(*args, c["grad_weights"])
+        assert float((true - r).abs().max()) > 1e-2
+        # finite differences side with the autograd gradient
+        x = c["logits"].double()
+        d = torch.zeros_like(x)
+        d[3, 1] = 1e-4
+        def f(z):
+            l, _, w, _ = O.topk_gating(z.float(), c["k"], c["capacity_factor"], c["min_capacity"])
+            return float(l.double() * 0.7 + (w.double() * c["grad_weights"].double()).sum())
+        fd = (f(x + d) - f(x - d)) / 2e-4
+        assert abs(fd - float(true[3, 1])) < 5e-2 * max(1.0, abs(fd))
