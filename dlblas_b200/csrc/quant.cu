@@ -332,6 +332,84 @@ int grid_for(long long total_threads) {
   return (int)blocks;
 }
 
+// ---- training-side un-permute (dlblas/kernels/permute/moe_triton_kernels.py) -----------------
+// out[t] = sum over k of prob[t, k] * in[row_id_map[k * T + t]] (entries -1 skipped), accumulated in
+// the tensor's own type with a rounding after every product and every add, as gather_kernel
+// (:229-271) does.  Without probs it is the plain sum of permute's backward (:140-167).
+template <typename T>
+__global__ void __launch_bounds__(THREADS) unpermute_kernel(const T* __restrict__ in, const int* __restrict__ row_id_map,
+                                                            const float* __restrict__ probs, long long tokens,
+                                                            int top_k, long long h, T* __restrict__ out) {
+  const long long vec_per_row = h / 8;
+  const long long total = tokens * vec_per_row;
+  for (long long u = (long long)blockIdx.x * THREADS + threadIdx.x; u < total; u += (long long)gridDim.x * THREADS) {
+    const long long t = u / vec_per_row;
+    const long long c = (u - t * vec_per_row) * 8;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    bool first = true;
+    for (int j = 0; j < top_k; ++j) {
+      const int row = __ldg(row_id_map + (long long)j * tokens + t);
+      if (row < 0) {
+        if (j == 0) first = false;      // the reference starts from zeros when slot 0 is unrouted
+        continue;
+      }
+      float v[8];
+      Vec8<T>::load(in + (long long)row * h + c, v);
+      if (probs != nullptr) {
+        const float p = to_f32<T>(from_f32<T>(__ldg(probs + t * top_k + j)));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = to_f32<T>(from_f32<T>(v[i] * p));
+      }
+      if (j == 0 && first) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = v[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = to_f32<T>(from_f32<T>(acc[i] + v[i]));
+      }
+    }
+    Vec8<T>::store(out + t * h + c, acc);
+  }
+}
+
+// Backward of the weighted un-permute (scatter_bwd_kernel_optimized, :427-478): one warp per token;
+// act_grad[row] = grad_out[t] * prob[t, k] (product in the tensors' type, stored as fp32),
+// prob_grad[t, k] = sum over columns of the type-rounded products grad_out[t] * fwd_in[row], in fp32.
+template <typename T>
+__global__ void __launch_bounds__(THREADS) unpermute_bwd_kernel(const T* __restrict__ grad_out,
+                                                                const T* __restrict__ fwd_in,
+                                                                const int* __restrict__ row_id_map,
+                                                                const float* __restrict__ probs, long long tokens,
+                                                                int top_k, long long h, float* __restrict__ act_grad,
+                                                                float* __restrict__ prob_grad) {
+  const int lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  for (int j = 0; j < top_k; ++j) {
+    const int row = __ldg(row_id_map + (long long)j * tokens + t);
+    float dot = 0.f;
+    if (row >= 0) {
+      const float p = to_f32<T>(from_f32<T>(__ldg(probs + t * top_k + j)));
+      for (long long c = lane * 8; c < h; c += 256) {
+        float go[8], fw[8];
+        Vec8<T>::load(grad_out + t * h + c, go);
+        Vec8<T>::load(fwd_in + (long long)row * h + c, fw);
+        float ag[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          ag[i] = to_f32<T>(from_f32<T>(go[i] * p));
+          dot += to_f32<T>(from_f32<T>(go[i] * fw[i]));
+        }
+        Vec8<float>::store(act_grad + (long long)row * h + c, ag);
+      }
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) prob_grad[t * top_k + j] = dot;
+  }
+}
+
 }  // namespace
 }  // namespace dlb
 
@@ -592,5 +670,64 @@ extern "C" int dlb_ep_dest_ranks(const void* ids, int ids_dtype, int64_t tokens,
                                                           num_local_experts, world, dest);
   count_launch();
   DLB_CHECK_LAUNCH("dest_ranks_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_unpermute(const void* in, int dtype, const int32_t* row_id_map, const float* probs, int64_t tokens,
+                             int top_k, int64_t h, void* out, void* stream) {
+  DLB_REQUIRE(tokens >= 0 && top_k > 0 && h > 0 && h % 8 == 0, DLB_ERR_INVALID,
+              "unpermute: bad sizes tokens=%lld top_k=%d h=%lld (h must be a multiple of 8)", (long long)tokens, top_k,
+              (long long)h);
+  if (tokens == 0) return DLB_OK;
+  DLB_REQUIRE(in && row_id_map && out, DLB_ERR_INVALID, "unpermute: null pointer");
+  DLB_REQUIRE((uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0, DLB_ERR_INVALID, "unpermute: misaligned tensors");
+  const long long total = tokens * (h / 8);
+  const int grid = (int)std::min<long long>(ceil_div(total, (long long)THREADS), (long long)sm_count() * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == DLB_BF16)
+    unpermute_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(in), row_id_map,
+                                                             probs, tokens, top_k, h,
+                                                             reinterpret_cast<__nv_bfloat16*>(out));
+  else if (dtype == DLB_F16)
+    unpermute_kernel<__half><<<grid, THREADS, 0, st>>>(reinterpret_cast<const __half*>(in), row_id_map, probs, tokens,
+                                                      top_k, h, reinterpret_cast<__half*>(out));
+  else if (dtype == DLB_F32)
+    unpermute_kernel<float><<<grid, THREADS, 0, st>>>(reinterpret_cast<const float*>(in), row_id_map, probs, tokens,
+                                                     top_k, h, reinterpret_cast<float*>(out));
+  else
+    return fail(DLB_ERR_INVALID, "unpermute: unsupported dtype %d", dtype);
+  count_launch();
+  DLB_CHECK_LAUNCH("unpermute_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_unpermute_bwd(const void* grad_out, const void* fwd_in, int dtype, const int32_t* row_id_map,
+                                 const float* probs, int64_t tokens, int top_k, int64_t h, float* act_grad,
+                                 float* prob_grad, void* stream) {
+  DLB_REQUIRE(tokens >= 0 && top_k > 0 && h > 0 && h % 8 == 0, DLB_ERR_INVALID,
+              "unpermute_bwd: bad sizes tokens=%lld top_k=%d h=%lld", (long long)tokens, top_k, (long long)h);
+  if (tokens == 0) return DLB_OK;
+  DLB_REQUIRE(grad_out && fwd_in && row_id_map && probs && act_grad && prob_grad, DLB_ERR_INVALID,
+              "unpermute_bwd: null pointer");
+  DLB_REQUIRE((uintptr_t)grad_out % 16 == 0 && (uintptr_t)fwd_in % 16 == 0 && (uintptr_t)act_grad % 16 == 0,
+              DLB_ERR_INVALID, "unpermute_bwd: misaligned tensors");
+  const int grid = (int)ceil_div(tokens, (long long)(THREADS / 32));
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == DLB_BF16)
+    unpermute_bwd_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(grad_out), reinterpret_cast<const __nv_bfloat16*>(fwd_in), row_id_map,
+        probs, tokens, top_k, h, act_grad, prob_grad);
+  else if (dtype == DLB_F16)
+    unpermute_bwd_kernel<__half><<<grid, THREADS, 0, st>>>(reinterpret_cast<const __half*>(grad_out),
+                                                          reinterpret_cast<const __half*>(fwd_in), row_id_map, probs,
+                                                          tokens, top_k, h, act_grad, prob_grad);
+  else if (dtype == DLB_F32)
+    unpermute_bwd_kernel<float><<<grid, THREADS, 0, st>>>(reinterpret_cast<const float*>(grad_out),
+                                                         reinterpret_cast<const float*>(fwd_in), row_id_map, probs,
+                                                         tokens, top_k, h, act_grad, prob_grad);
+  else
+    return fail(DLB_ERR_INVALID, "unpermute_bwd: unsupported dtype %d", dtype);
+  count_launch();
+  DLB_CHECK_LAUNCH("unpermute_bwd_kernel");
   return DLB_OK;
 }

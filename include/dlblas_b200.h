@@ -216,6 +216,19 @@ DLB_API int dlb_p2p_unpack_meta(const int32_t* meta, int meta_ints, int top_k, c
 DLB_API int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32_t* counts, int world, int my_rank,
                       int64_t region_rows, const void* const* peer_dst, void* stream);
 
+/* ---- training-side permutation (dlblas/kernels/permute/moe_triton_kernels.py) ------------------
+ * row_id_map int32 [top_k * tokens], k-major: destination row of (token, slot) in the permuted tensor, -1 for
+ * unrouted slots.  Permute forward is dlb_sort_by_expert + dlb_permute_rows.
+ * dlb_unpermute = moe_recover_topk_op_triton (:274-301) and, with probs = NULL, moe_permute_topk_bwd_op
+ * (:190-213): out[t] = sum_k prob[t,k] * in[row_id_map[k,t]], rounded to the tensor type after every product
+ * and add.  dlb_unpermute_bwd = moe_recover_topk_bwd_op_triton (:480-528): act_grad fp32 [rows, h] (rows that no
+ * slot maps to are left untouched: zero them first), prob_grad fp32 [tokens, top_k]. */
+DLB_API int dlb_unpermute(const void* in, int dtype, const int32_t* row_id_map, const float* probs, int64_t tokens,
+                  int top_k, int64_t h, void* out, void* stream);
+DLB_API int dlb_unpermute_bwd(const void* grad_out, const void* fwd_in, int dtype, const int32_t* row_id_map,
+                      const float* probs, int64_t tokens, int top_k, int64_t h, float* act_grad, float* prob_grad,
+                      void* stream);
+
 /* ---- expert-parallel load balancing ------------------------------------------------
  * map_logic_to_physical_idx_hash_random (dlblas/kernels/moe.py:524-579): every (token, slot) of topk_idx
  * [tokens, top_k] (int32 or int64) is sent to one of the logcnt[e] physical replicas log2phy[e, 0..) of its

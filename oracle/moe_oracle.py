@@ -480,3 +480,50 @@ def topk_gating_bwd_reference_hp(logits: torch.Tensor, k: int, capacity_factor: 
     add_2 = (scat * masks).sum(dim=0) + ce * torch.as_tensor(grad_l_aux, dtype=torch.float32) * e / t
     dx = gates * add_2
     return dx - gates * dx.sum(dim=1, keepdim=True)
+
+
+def permute_topk(tokens: torch.Tensor, indices: torch.Tensor):
+    """dlblas/kernels/permute/moe_triton_kernels.py:17-137 (the torch model is permute_torch of
+    tests/kernels/permute/permute_triton.py:23-38): rows in stable expert order, slots routed to -1 dropped.
+    Returns (permuted [routed, H], row_id_map int32 [k*T] k-major with -1 for dropped slots, sorted slot ids)."""
+    t, k = indices.shape
+    flat = indices.reshape(-1).to(torch.int64)
+    order = torch.argsort(flat, stable=True)
+    dropped = int((flat < 0).sum())
+    kept = order[dropped:]
+    permuted = tokens.index_select(0, kept // k)
+    rmap = torch.full((k * t,), -1, dtype=torch.int32)
+    rmap[(kept % k) * t + kept // k] = torch.arange(kept.numel(), dtype=torch.int32)
+    return permuted, rmap, order
+
+
+def unpermute_topk(permuted: torch.Tensor, row_id_map: torch.Tensor, probs, tokens: int, top_k: int) -> torch.Tensor:
+    """gather_kernel (:229-271): accumulate in the tensor dtype, rounding after every product and add."""
+    dt = permuted.dtype
+    out = torch.zeros(tokens, permuted.shape[1], dtype=dt)
+    rmap = row_id_map.view(top_k, tokens).to(torch.int64)
+    for j in range(top_k):
+        rows = rmap[j]
+        ok = rows >= 0
+        frag = permuted[rows.clamp(min=0)]
+        if probs is not None:
+            frag = (frag * probs[:, j:j + 1].to(dt)).to(dt)
+        frag = torch.where(ok[:, None], frag, torch.zeros_like(frag))
+        out = frag if j == 0 else (out + frag).to(dt)
+    return out
+
+
+def unpermute_topk_bwd(grad_out: torch.Tensor, fwd_in: torch.Tensor, row_id_map: torch.Tensor, probs: torch.Tensor):
+    """scatter_bwd_kernel_optimized (:427-478): act_grad fp32 = dtype(grad_out * dtype(prob)) scattered to the
+    permuted rows; prob_grad[t, k] = fp32 sum of dtype(grad_out[t] * fwd_in[row])."""
+    t, k = probs.shape
+    dt = grad_out.dtype
+    rmap = row_id_map.view(k, t).to(torch.int64)
+    act = torch.zeros(fwd_in.shape, dtype=torch.float32)
+    pg = torch.zeros(t, k, dtype=torch.float32)
+    for j in range(k):
+        rows = rmap[j]
+        ok = rows >= 0
+        act[rows[ok]] = (grad_out[ok] * probs[ok, j:j + 1].to(dt)).to(dt).to(torch.float32)
+        pg[ok, j] = (grad_out[ok] * fwd_in[rows[ok]]).to(dt).to(torch.float32).sum(dim=1)
+    return act, pg

@@ -241,6 +241,42 @@ def gold_topk_gating_bwd(ref, out):
     print("topk_gating_bwd:", len(cases), "cases", [c.get("hp_error", "hp ok") for c in cases])
 
 
+def gold_permute(ref, out):
+    """Training-side permutation (dlblas/kernels/permute/moe_triton_kernels.py): permute / un-permute forward
+    and backward on fp32 data (no low-precision casts, which the interpreter rounds differently)."""
+    sys.modules.setdefault("dlblas.kernels.permute", types.ModuleType("dlblas.kernels.permute")).__path__ = [
+        os.path.join(ref, "dlblas", "kernels", "permute")]
+    import dlblas.kernels.permute.moe_triton_kernels as P
+    cases = []
+    g = torch.Generator().manual_seed(31)
+    for (t, k, e, h, neg) in [(37, 2, 8, 64, False), (50, 4, 16, 128, True)]:
+        x = torch.randn(t, h, generator=g)
+        ids = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]).to(torch.int32)
+        if neg:
+            ids[torch.rand(t, k, generator=g) < 0.2] = -1
+        n_neg = int((ids == -1).sum())
+        n_out = t * k - n_neg
+        permuted = torch.zeros(n_out, h)
+        row_id_map = torch.full((t * k,), -1, dtype=torch.int32)   # the reference leaves unrouted entries unwritten
+        ws = []
+        perm, rmap, sorted_ids, ws = P.moe_permute_topk_op_triton(x, ids, n_out, ws, t * k, n_neg, permuted, row_id_map)
+        probs = torch.rand(t, k, generator=g)
+        y = torch.randn(n_out, h, generator=g)
+        un = P.moe_recover_topk_op_triton(y, rmap, probs, t, k)
+        un_noprob = P.moe_recover_topk_op_triton(y, rmap, None, t, k)
+        go = torch.randn(t, h, generator=g)
+        act_grad, prob_grad = P.moe_recover_topk_bwd_op_triton(go, y, rmap, probs)
+        gperm = torch.randn(n_out, h, generator=g)
+        case = dict(x=x, ids=ids, permuted=perm.clone(), row_id_map=rmap.clone(), sorted_row_id=sorted_ids.clone(),
+                    probs=probs, y=y, unpermuted=un.clone(), unpermuted_noprob=un_noprob.clone(), grad_out=go,
+                    act_grad=act_grad.clone(), prob_grad=prob_grad.clone(), grad_permuted=gperm)
+        if not neg:
+            case["permute_bwd"] = P.moe_permute_topk_bwd_op(gperm, sorted_ids, (t, h), k).clone()
+        cases.append(case)
+    torch.save(cases, os.path.join(out, "permute.pt"))
+    print("permute:", len(cases), "cases")
+
+
 def gold_scatter_gather(ref, out):
     from dlblas.kernels.fused_moe_v3 import ep_gather, ep_scatter
     g = torch.Generator().manual_seed(8)
@@ -350,7 +386,7 @@ def main():
     a = ap.parse_args()
     install_shim(a.reference)
     todo = [gold_sort, gold_quant, gold_gemm, gold_grouped, gold_activation, gold_grouped_topk,
-            gold_topk_gating, gold_topk_gating_bwd, gold_scatter_gather, gold_eplb]
+            gold_topk_gating, gold_topk_gating_bwd, gold_scatter_gather, gold_eplb, gold_permute]
     for fn in todo:
         if a.only and a.only not in fn.__name__:
             continue
