@@ -527,3 +527,40 @@ def unpermute_topk_bwd(grad_out: torch.Tensor, fwd_in: torch.Tensor, row_id_map:
         act[rows[ok]] = (grad_out[ok] * probs[ok, j:j + 1].to(dt)).to(dt).to(torch.float32)
         pg[ok, j] = (grad_out[ok] * fwd_in[rows[ok]]).to(dt).to(torch.float32).sum(dim=1)
     return act, pg
+
+
+def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: int, pad_sorted_ids: bool = False):
+    """dlblas/kernels/moe_align_block_size.py:138-210 (docstring example :160-176): per expert, the flat
+    slot indices in ascending order, padded with `numel` to a multiple of block_size; expert id per block
+    (0 past the end); total padded length."""
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    numel = flat.numel()
+    max_padded = numel + num_experts * (block_size - 1)
+    if pad_sorted_ids:
+        max_padded = (max_padded + block_size - 1) // block_size * block_size
+    sorted_ids = torch.full((max_padded,), numel, dtype=torch.int32)
+    expert_ids = torch.zeros(((max_padded + block_size - 1) // block_size,), dtype=torch.int32)
+    off = 0
+    for e in range(num_experts):
+        slots = torch.nonzero(flat == e).flatten()
+        n = int(slots.numel())
+        sorted_ids[off:off + n] = slots.to(torch.int32)
+        blocks = (n + block_size - 1) // block_size
+        expert_ids[off // block_size: off // block_size + blocks] = e
+        off += blocks * block_size
+    return sorted_ids, expert_ids, torch.tensor([off], dtype=torch.int32)
+
+
+def fused_moe_v2(x, w1, w1_s, w2, w2_s, topk_weights, topk_ids, group_size: int = 128, out_dtype=torch.bfloat16):
+    """dlblas/kernels/fused_moe_v2.py:323-471 for block-quantised FP8: the same pipeline as
+    fused_moe_blocked_fp8 with the `max(absmax, 1e-10) / 448` activation scales of
+    per_token_group_quant_fp8 (moe_kernel_prepare_input, :214-225)."""
+    t, k = topk_ids.shape
+    x_q, x_s = per_token_group_quant_fp8(x, group_size)
+    sorted_idx, exp_start, exp_end = stable_sort_by_expert(topk_ids, w1.shape[0])
+    c1 = grouped_gemm(x_q, x_s, w1, w1_s, sorted_idx, exp_start, exp_end, top_k=k, reindex_a=True, reindex_c=False,
+                      num_rows_c=t * k, out_dtype=out_dtype)
+    h_q, h_s = per_token_group_quant_fp8(silu_and_mul(c1), group_size)
+    y = grouped_gemm(h_q, h_s, w2, w2_s, sorted_idx, exp_start, exp_end, topk_weights.reshape(-1).to(torch.float32),
+                     top_k=1, reindex_a=False, reindex_c=True, num_rows_c=t * k, out_dtype=out_dtype)
+    return y.view(t, k, -1).sum(dim=1)

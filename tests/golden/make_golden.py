@@ -277,6 +277,24 @@ def gold_permute(ref, out):
     print("permute:", len(cases), "cases")
 
 
+def gold_align(ref, out):
+    """moe_align_block_size (dlblas/kernels/moe_align_block_size.py:138-210) under the interpreter."""
+    from dlblas.kernels.moe_align_block_size import moe_align_block_size
+    cases = []
+    # the worked example of the function's own docstring (:160-176), shifted to 0-based expert ids
+    ids = torch.tensor([[1, 2, 3], [0, 1, 3], [0, 2, 3], [0, 1, 2]], dtype=torch.int32)
+    todo = [(ids, 4, 4, False)]
+    g = torch.Generator().manual_seed(41)
+    for (t, k, e, bs, pad) in [(40, 2, 8, 16, False), (65, 4, 16, 64, True), (9, 8, 32, 128, False)]:
+        todo.append((torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]).to(torch.int32), bs, e, pad))
+    for (ids, bs, e, pad) in todo:
+        s_ids, e_ids, n_post = moe_align_block_size(ids.clone(), bs, e, e, None, pad)
+        cases.append(dict(topk_ids=ids, block_size=bs, num_experts=e, pad_sorted_ids=pad, sorted_ids=s_ids.clone(),
+                          expert_ids=e_ids.clone(), num_tokens_post_pad=n_post.clone()))
+    torch.save(cases, os.path.join(out, "align_block.pt"))
+    print("align_block:", len(cases), "cases; docstring example ->", cases[0]["sorted_ids"].tolist())
+
+
 def gold_scatter_gather(ref, out):
     from dlblas.kernels.fused_moe_v3 import ep_gather, ep_scatter
     g = torch.Generator().manual_seed(8)
@@ -386,7 +404,7 @@ def main():
     a = ap.parse_args()
     install_shim(a.reference)
     todo = [gold_sort, gold_quant, gold_gemm, gold_grouped, gold_activation, gold_grouped_topk,
-            gold_topk_gating, gold_topk_gating_bwd, gold_scatter_gather, gold_eplb, gold_permute]
+            gold_topk_gating, gold_topk_gating_bwd, gold_scatter_gather, gold_eplb, gold_permute, gold_align]
     for fn in todo:
         if a.only and a.only not in fn.__name__:
             continue
