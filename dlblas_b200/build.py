@@ -13,8 +13,8 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OUT = os.path.join(PKG, "_dlblas_b200.so")
-SOURCES = ["abi.cu", "sort.cu", "quant.cu", "route.cu", "p2p.cu", "gemm_fp8.cu"]
-HEADERS = ["common.cuh", "sort.cuh", os.path.join("..", "..", "include", "dlblas_b200.h")]
+SOURCES = ["abi.cu", "sort.cu", "quant.cu", "route.cu", "p2p.cu", "gemm_fp8.cu", "gemm_bf16.cu"]
+HEADERS = ["common.cuh", "sort.cuh", "umma.cuh", os.path.join("..", "..", "include", "dlblas_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

@@ -1,0 +1,362 @@
+// Grouped (and dense) GEMM on 16-bit operands for sm_100a: C[rows of group g] = A[rows of g] * B[g]^T with
+// A [M, K] and B [G, N, K] both K-major, fp32 accumulation in TMEM over the whole K, one rounding to the
+// 16-bit output (m_grouped_gemm of dlblas/kernels/grouped_gemm/BF16/m_grouped_gemm.py:235-352, trans_b = True).
+//
+// Same skeleton as the block-scaled FP8 kernel, without its per-K-block promotion:
+//   warp 8   TMA producer: A tile [128 x 128 B] and B tile [256 x 128 B] per 64-element K block
+//   warp 9   tcgen05.mma kind::f16 (128 x 256 x 16, four per K block), whole K into one of two TMEM accumulators
+//   warps 0-7  drain a finished accumulator (tcgen05.ld), round to the output type into a padded staging tile
+//   warps 10-11  send the staging rows out with one bulk copy each
+// While a tile is drained and stored the MMA warp already fills the other accumulator.  Waits are bounded.
+#include "umma.cuh"
+
+namespace dlb {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int A_STAGE_BYTES = BM * UMMA_BK_BYTES;
+constexpr int B_STAGE_BYTES = BN * UMMA_BK_BYTES;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int STAGES = 3;
+constexpr int DRAIN_WARPS = 8;
+constexpr int PRODUCER_WARP = 8;
+constexpr int MMA_WARP = 9;
+constexpr int STORE_WARP0 = 10;
+constexpr int STORE_WARPS = 2;
+constexpr int NUM_THREADS = 384;
+constexpr int TMEM_COLS = 512;
+constexpr int TMEM_BUFS = 2;
+constexpr int STAGING_ROW_BYTES = BN * 2 + 16;
+constexpr int STAGING_OFF = STAGES * STAGE_BYTES;
+constexpr int BAR_OFF = STAGING_OFF + BM * STAGING_ROW_BYTES;
+constexpr int NUM_BARS = 2 * STAGES + 2 * TMEM_BUFS + 3;
+constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
+constexpr int SMEM_BYTES = MISC_OFF + 16 + 1024;
+
+struct Args16 {
+  void* c;
+  long long ldc;
+  const int4* tiles;     // nullptr: one group, M tiles derived from m
+  int m, n, k_bytes;
+  int num_m_tiles_static, num_n_tiles;
+  uint32_t idesc;
+  int* status;
+  unsigned long long timeout_cycles;
+};
+
+// kind::f16: fp32 accumulate, A and B K-major, both of format `fmt` (0 = fp16, 1 = bf16), M = 128, N = BN
+constexpr uint32_t make_idesc16(uint32_t fmt) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+struct Tile16 {
+  int e, row0, rows, n0;
+};
+__device__ __forceinline__ Tile16 decode16(const Args16& g, int t) {
+  Tile16 ti;
+  const int m_tile = t / g.num_n_tiles;
+  const int n_tile = t - m_tile * g.num_n_tiles;
+  if (g.tiles != nullptr) {
+    const int4 v = __ldg(g.tiles + 1 + m_tile);
+    ti.e = v.x;
+    ti.row0 = v.y;
+    ti.rows = v.z;
+  } else {
+    ti.e = 0;
+    ti.row0 = m_tile * BM;
+    ti.rows = min(BM, g.m - ti.row0);
+  }
+  ti.n0 = n_tile * BN;
+  return ti;
+}
+
+template <typename T> __device__ __forceinline__ uint32_t pack16(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack16<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack16<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Args16 g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + BAR_OFF;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + TMEM_BUFS + b); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 2 * TMEM_BUFS);
+  const uint32_t staged_bar = drain_bar + 8u;
+  const uint32_t sfree_bar = drain_bar + 16u;
+  uint8_t* staging = smem + STAGING_OFF;
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + MISC_OFF);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + MISC_OFF + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kblocks = (g.k_bytes + UMMA_BK_BYTES - 1) / UMMA_BK_BYTES;
+  const int num_m_tiles = g.tiles != nullptr ? __ldg(reinterpret_cast<const int*>(g.tiles)) : g.num_m_tiles_static;
+  const int total_tiles = num_m_tiles * g.num_n_tiles;
+  const unsigned long long limit = g.timeout_cycles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < TMEM_BUFS; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), DRAIN_WARPS);
+    }
+    mbar_init(drain_bar, 1);
+    mbar_init(staged_bar, DRAIN_WARPS);
+    mbar_init(sfree_bar, STORE_WARPS);
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(const_cast<uint32_t*>(tmem_holder))),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == PRODUCER_WARP) {
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const Tile16 ti = decode16(g, t);
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, abort_flag, limit)) {
+          ok = false;
+          break;
+        }
+        const uint32_t a_dst = smem_base + s * STAGE_BYTES;
+        const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+        if (elect_one()) {
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, kb * UMMA_BK_BYTES, ti.row0, full_bar(s));
+          tma_load_2d(b_dst, &tmap_b, kb * UMMA_BK_BYTES, ti.e * g.n + ti.n0, full_bar(s));
+          tma_load_2d(b_dst + 128 * UMMA_BK_BYTES, &tmap_b, kb * UMMA_BK_BYTES, ti.e * g.n + ti.n0 + 128, full_bar(s));
+        }
+        __syncwarp();
+      }
+    }
+    if (!ok) {
+      const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0u;
+      for (uint32_t i = first; i < it; ++i)
+        mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1u, abort_flag + 1, 40000000ull);
+    }
+  } else if (warp == MMA_WARP) {
+    uint32_t it = 0, tile_no = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
+      const int b = tile_no % TMEM_BUFS;
+      if (!mbar_wait(tempty_bar(b), ((tile_no / TMEM_BUFS) & 1u) ^ 1u, abort_flag, limit)) {
+        ok = false;
+        break;
+      }
+      const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, abort_flag, limit)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_base + s * STAGE_BYTES;
+        const uint64_t a_desc = make_smem_desc(a_addr);
+        const uint64_t b_desc = make_smem_desc(a_addr + A_STAGE_BYTES);
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < UMMA_BK_BYTES / 32; ++kk)
+            tc_mma_f16(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(empty_bar(s));
+          if (kb == kblocks - 1) tc_commit(tfull_bar(b));
+        }
+        __syncwarp();
+      }
+    }
+    if (!ok) {
+      if (elect_one()) tc_commit(drain_bar);
+      __syncwarp();
+      mbar_wait(drain_bar, 0, abort_flag + 1, 40000000ull);
+    }
+  } else if (warp >= STORE_WARP0) {
+    const int ew = warp - STORE_WARP0;
+    uint32_t tile_no = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
+      const Tile16 ti = decode16(g, t);
+      if (!mbar_wait(staged_bar, tile_no & 1u, abort_flag, limit)) {
+        ok = false;
+        break;
+      }
+      const uint32_t bytes = (uint32_t)min(BN, g.n - ti.n0) * 2u;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int row = ew * 64 + i * 32 + lane;
+        if (row < ti.rows)
+          bulk_store(reinterpret_cast<T*>(g.c) + ((long long)ti.row0 + row) * g.ldc + ti.n0,
+                     smem_u32(staging + row * STAGING_ROW_BYTES), bytes);
+      }
+      bulk_commit();
+      bulk_wait_read();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sfree_bar);
+    }
+    bulk_wait_all();
+  } else {
+    // ---- drain warps ----
+    const int wg = warp >> 2;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    uint8_t* srow = staging + r * STAGING_ROW_BYTES + wg * 128 * 2;
+    uint32_t tile_no = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
+      const int b = tile_no % TMEM_BUFS;
+      if (!mbar_wait(tfull_bar(b), (tile_no / TMEM_BUFS) & 1u, abort_flag, limit) ||
+          !mbar_wait(sfree_bar, (tile_no & 1u) ^ 1u, abort_flag, limit)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t col0 = lane_addr + (uint32_t)(b * BN + wg * 128);
+      uint32_t s0[32], s1[32];
+      tmem_ld32(col0, s0);
+      tmem_ld32(col0 + 32, s1);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        tmem_ld_wait(s0, s1);
+        if (q == 1) {
+          // the whole accumulator is in registers: the MMA warp may reuse it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(b));
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t (&s)[32] = half == 0 ? s0 : s1;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            v.x = pack16<T>(__uint_as_float(s[j]), __uint_as_float(s[j + 1]));
+            v.y = pack16<T>(__uint_as_float(s[j + 2]), __uint_as_float(s[j + 3]));
+            v.z = pack16<T>(__uint_as_float(s[j + 4]), __uint_as_float(s[j + 5]));
+            v.w = pack16<T>(__uint_as_float(s[j + 6]), __uint_as_float(s[j + 7]));
+            *reinterpret_cast<uint4*>(srow + ((2 * q + half) * 32 + j) * 2) = v;
+          }
+        }
+        if (q == 0) {
+          tmem_ld32(col0 + 64, s0);
+          tmem_ld32(col0 + 96, s1);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(staged_bar);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0 && g.status != nullptr) atomicExch(g.status, DLB_STATUS_TIMEOUT);
+  if (warp == MMA_WARP) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+template <typename T>
+int launch16(const CUtensorMap& ma, const CUtensorMap& mb, const Args16& g, int grid, cudaStream_t st) {
+  auto kern = gemm16_kernel<T>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES),
+                        "cudaFuncSetAttribute(gemm16_kernel)");
+    if (rc != DLB_OK) return rc;
+    configured[dev] = true;
+  }
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, g);
+  count_launch();
+  DLB_CHECK_LAUNCH("gemm16_kernel");
+  return DLB_OK;
+}
+
+}  // namespace
+}  // namespace dlb
+
+using namespace dlb;
+
+extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t rows, int num_groups, int64_t n,
+                                      int64_t k, const int32_t* tiles, int max_tiles, void* c, int64_t ldc,
+                                      int32_t* status, void* stream) {
+  DLB_REQUIRE(rows >= 0 && n > 0 && k > 0 && num_groups > 0, DLB_ERR_INVALID,
+              "grouped_gemm_16bit: bad sizes rows=%lld n=%lld k=%lld groups=%d", (long long)rows, (long long)n,
+              (long long)k, num_groups);
+  DLB_REQUIRE(dtype == DLB_BF16 || dtype == DLB_F16, DLB_ERR_INVALID, "grouped_gemm_16bit: dtype must be bf16 or fp16");
+  DLB_REQUIRE(k % 8 == 0 && n % 8 == 0 && ldc % 8 == 0, DLB_ERR_INVALID,
+              "grouped_gemm_16bit: k=%lld, n=%lld and ldc=%lld must be multiples of 8 (16-byte rows)", (long long)k,
+              (long long)n, (long long)ldc);
+  DLB_REQUIRE(rows < (1ll << 31) && (long long)num_groups * n < (1ll << 31) && 2 * k < (1ll << 31), DLB_ERR_INVALID,
+              "grouped_gemm_16bit: size too large");
+  DLB_REQUIRE(tiles != nullptr || num_groups == 1, DLB_ERR_INVALID, "grouped_gemm_16bit: several groups need a tile list");
+  if (rows == 0 || (tiles != nullptr && max_tiles == 0)) return DLB_OK;
+  DLB_REQUIRE(a && b && c, DLB_ERR_INVALID, "grouped_gemm_16bit: null pointer");
+  DLB_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 16 == 0) &&
+                  ((uintptr_t)tiles % 16 == 0),
+              DLB_ERR_INVALID, "grouped_gemm_16bit: a, b, c and tiles must be 16-byte aligned");
+  int rc = check_device();
+  if (rc != DLB_OK) return rc;
+  CUtensorMap ma, mb;
+  if ((rc = make_map(&ma, a, (uint64_t)rows, (uint64_t)(2 * k))) != DLB_OK) return rc;
+  if ((rc = make_map(&mb, b, (uint64_t)num_groups * (uint64_t)n, (uint64_t)(2 * k))) != DLB_OK) return rc;
+  Args16 g = {};
+  g.c = c;
+  g.ldc = ldc;
+  g.tiles = reinterpret_cast<const int4*>(tiles);
+  g.m = (int)rows;
+  g.n = (int)n;
+  g.k_bytes = (int)(2 * k);
+  g.num_m_tiles_static = (int)ceil_div(rows, (int64_t)BM);
+  g.num_n_tiles = (int)ceil_div(n, (int64_t)BN);
+  g.idesc = make_idesc16(dtype == DLB_BF16 ? 1u : 0u);
+  g.status = status;
+  g.timeout_cycles = DEFAULT_TIMEOUT_CYCLES;
+  const int sms = sm_count();
+  const long long total = (long long)(tiles != nullptr ? max_tiles : g.num_m_tiles_static) * g.num_n_tiles;
+  const int grid = (int)(total < sms ? total : sms);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == DLB_BF16) return launch16<__nv_bfloat16>(ma, mb, g, grid, st);
+  return launch16<__half>(ma, mb, g, grid, st);
+}

@@ -33,9 +33,7 @@
 // All mbarrier waits are bounded (about 2 s of SM clock cycles): a wait that exceeds its limit raises a CTA-wide
 // abort flag, every role leaves its loop, the status word is set to DLB_STATUS_TIMEOUT
 // and the kernel returns after draining what it issued.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "umma.cuh"
 
 namespace dlb {
 namespace {
@@ -73,165 +71,6 @@ struct GemmArgs {
   int* status;
   unsigned long long timeout_cycles;
 };
-
-// ---- PTX wrappers ------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// One poll of the barrier.  The suspend-time hint lets the hardware park the warp until the
-// phase completes (or the hint, in ns, runs out) instead of spinning: a spinning role would
-// take issue slots from the promotion warps that share its scheduler.
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(1000000u)
-      : "memory");
-  return ok;
-}
-// Bounded wait.  Returns false when the CTA is aborting (set by this or another thread).
-// The time limit is counted in SM clock cycles (clock64 is a register read; the global
-// nanosecond timer costs hundreds of cycles per read and these waits sit on the critical path
-// of every K block).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned long long limit_cycles) {
-  if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag) return false;
-    const long long now = clock64();
-    if (t0 == 0) {
-      t0 = now;
-    } else if ((unsigned long long)(now - t0) > limit_cycles) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-
-// True in exactly one lane of a converged warp.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// 32 lanes x 32 consecutive columns, one fp32 per register.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-// Waits for all of this thread's outstanding tcgen05.ld.  Both staging buffers are listed as
-// read-write operands so the compiler cannot schedule arithmetic on them above the wait.
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[32], uint32_t (&b)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
-                 "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]),
-                 "+r"(a[16]), "+r"(a[17]), "+r"(a[18]), "+r"(a[19]), "+r"(a[20]), "+r"(a[21]), "+r"(a[22]),
-                 "+r"(a[23]), "+r"(a[24]), "+r"(a[25]), "+r"(a[26]), "+r"(a[27]), "+r"(a[28]), "+r"(a[29]),
-                 "+r"(a[30]), "+r"(a[31]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]),
-                 "+r"(b[6]), "+r"(b[7]), "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]),
-                 "+r"(b[14]), "+r"(b[15]), "+r"(b[16]), "+r"(b[17]), "+r"(b[18]), "+r"(b[19]), "+r"(b[20]),
-                 "+r"(b[21]), "+r"(b[22]), "+r"(b[23]), "+r"(b[24]), "+r"(b[25]), "+r"(b[26]), "+r"(b[27]),
-                 "+r"(b[28]), "+r"(b[29]), "+r"(b[30]), "+r"(b[31])
-               :
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait_plain() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Two fp32 FMAs per instruction (sm_100): d.xy = a.xy * b.xy + d.xy on packed register pairs.
-__device__ __forceinline__ void fma2(uint64_t& d, uint32_t a_lo, uint32_t a_hi, uint64_t b) {
-  uint64_t a;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "r"(a_lo), "r"(a_hi));
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
-}
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-
-// One row of the staging tile -> global memory, asynchronously (both addresses 16-byte aligned,
-// size a multiple of 16).
-__device__ __forceinline__ void bulk_store(void* gdst, uint32_t ssrc, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-               ::"l"(__cvta_generic_to_global(gdst)), "r"(ssrc), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// all earlier bulk stores of this thread have read their shared-memory source
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// all earlier bulk stores of this thread are complete
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-template <int N> __device__ __forceinline__ void reg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N> __device__ __forceinline__ void reg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-
-// K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);  // start address
-  d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                        // descriptor version (Blackwell)
-  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
-  return d;
-}
 
 // kind::f8f6f4, A and B e4m3 K-major, fp32 accumulate, M = 128, N = bn.
 __host__ __device__ constexpr uint32_t make_idesc(int bn) {
@@ -747,38 +586,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   }
 }
 
-// ---- host side -----------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// 2-D map over a row-major [rows, k] e4m3 matrix, box = 128 rows x 128 bytes, 128 B swizzle.
-int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (enc == nullptr) return fail(DLB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  const cuuint64_t gdim[2] = {k, rows};
-  const cuuint64_t gstride[1] = {k};
-  const cuuint32_t box[2] = {BK, 128};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(DLB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return DLB_OK;
-}
-
 template <int BN, int MODE, typename OutT>
 int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int grid, cudaStream_t st) {
   auto kern = gemm_fp8_kernel<BN, MODE, OutT>;
@@ -815,21 +622,6 @@ int launch_typed(int bn, int c_dtype, const CUtensorMap& ma, const CUtensorMap& 
   return fail(DLB_ERR_INVALID, "unsupported output dtype %d for this GEMM epilogue", c_dtype);
 }
 
-int check_device() {
-  static int ok[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 64 && ok[dev] == 1) return DLB_OK;
-  cudaDeviceProp prop;
-  int rc = check_cuda(cudaGetDeviceProperties(&prop, dev), "cudaGetDeviceProperties");
-  if (rc != DLB_OK) return rc;
-  if (prop.major != 10) return fail(DLB_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only",
-                                    dev, prop.major, prop.minor);
-  if (dev < 64) ok[dev] = 1;
-  return DLB_OK;
-}
-
-constexpr unsigned long long DEFAULT_TIMEOUT_CYCLES = 4000000000ull;  // about 2 s per barrier wait
 
 }  // namespace
 }  // namespace dlb

@@ -1,0 +1,39 @@
+"""m_grouped_gemm (dlblas/kernels/grouped_gemm/BF16/m_grouped_gemm.py:235-352 of the reference):
+C[rows of group g] = A[rows of g] @ B[g] for contiguous row groups of sizes `size_per_group`.
+
+The tcgen05 kernel wants both operands K-major, i.e. B as [G, N, K] (`trans_b=True`); with `trans_b=False`
+(B [G, K, N]) the weights are transposed once per call, an extra pass over B.  Tile list and group offsets are
+built on the device; nothing synchronises with the host."""
+import torch
+from torch import Tensor
+
+from .... import ops
+from ...._C import check, check_status, dtype_code, lib, ptr, require_cuda, status_word, stream  # noqa: F401
+
+
+def m_grouped_gemm(A: Tensor, B: Tensor, size_per_group: torch.Tensor, trans_b: bool = False, numSM: int = -1) -> Tensor:
+    assert A.dim() == 2
+    assert B.dim() == 3
+    require_cuda(A, B, size_per_group)
+    M, K = A.shape
+    assert A.stride(-1) == 1, "Please make sure A is K-major"
+    assert A.dtype == B.dtype and A.dtype in (torch.bfloat16, torch.float16)
+    if trans_b:
+        num_groups, N, BK = B.shape
+        Bt = B.contiguous()
+    else:
+        num_groups, BK, N = B.shape
+        Bt = B.transpose(1, 2).contiguous()
+    assert BK == K, "K of A should be equal to K of B"
+    assert size_per_group.numel() == num_groups
+    A = A.contiguous()
+    C = A.new_empty(M, N)
+    if M == 0:
+        return C
+    ends = torch.cumsum(size_per_group.to(torch.int64), 0)
+    starts = ends - size_per_group.to(torch.int64)
+    max_tiles = M // 128 + num_groups
+    tiles = ops.build_tiles(starts, ends, 0, num_groups, max_tiles)
+    check(lib().dlb_grouped_gemm_16bit(ptr(A), ptr(Bt), dtype_code(A.dtype), M, num_groups, N, K, ptr(tiles), max_tiles,
+                                       ptr(C), N, ptr(status_word(A.device)), stream(A.device)))
+    return C

@@ -216,6 +216,15 @@ DLB_API int dlb_p2p_unpack_meta(const int32_t* meta, int meta_ints, int top_k, c
 DLB_API int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32_t* counts, int world, int my_rank,
                       int64_t region_rows, const void* const* peer_dst, void* stream);
 
+/* ---- 16-bit grouped GEMM -----------------------------------------------------------------
+ * m_grouped_gemm with trans_b = True (dlblas/kernels/grouped_gemm/BF16/m_grouped_gemm.py:235-352):
+ * c[row, :] = a[row, :] * b[g]^T for the rows of group g; a [rows, k] and b [num_groups, n, k] bf16 or fp16,
+ * K-major; c [rows, ldc] of the same type, fp32 accumulation.  `tiles` is the tile list of
+ * dlb_moe_build_tiles over the groups' row ranges (NULL: one group, dense).  k, n, ldc multiples of 8. */
+DLB_API int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t rows, int num_groups, int64_t n,
+                           int64_t k, const int32_t* tiles, int max_tiles, void* c, int64_t ldc, int32_t* status,
+                           void* stream);
+
 /* ---- training-side permutation (dlblas/kernels/permute/moe_triton_kernels.py) ------------------
  * row_id_map int32 [top_k * tokens], k-major: destination row of (token, slot) in the permuted tensor, -1 for
  * unrouted slots.  Permute forward is dlb_sort_by_expert + dlb_permute_rows.

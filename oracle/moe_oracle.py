@@ -564,3 +564,14 @@ def fused_moe_v2(x, w1, w1_s, w2, w2_s, topk_weights, topk_ids, group_size: int 
     y = grouped_gemm(h_q, h_s, w2, w2_s, sorted_idx, exp_start, exp_end, topk_weights.reshape(-1).to(torch.float32),
                      top_k=1, reindex_a=False, reindex_c=True, num_rows_c=t * k, out_dtype=out_dtype)
     return y.view(t, k, -1).sum(dim=1)
+
+
+def m_grouped_gemm(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tensor, trans_b: bool = False) -> torch.Tensor:
+    """dlblas/kernels/grouped_gemm/BF16/m_grouped_gemm.py:235-352 against its ground truth `gmm`
+    (utils.py:77-86): per group, fp32 accumulation of 16-bit operands, one rounding to the operand type."""
+    out, start = [], 0
+    for i, size in enumerate(size_per_group.tolist()):
+        rhs = b[i].t() if trans_b else b[i]
+        out.append((a[start:start + size].to(torch.float32) @ rhs.to(torch.float32)).to(a.dtype))
+        start += size
+    return torch.cat(out) if out else a.new_empty(0, b.shape[1] if trans_b else b.shape[2])
