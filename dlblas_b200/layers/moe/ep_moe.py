@@ -44,12 +44,34 @@ class FusedMoENormal:
                                                       expert_alignment=expert_alignment)
         # Exchange backend: "p2p" = in-kernel stores into the peers' memory (default with more than one
         # rank), "nccl" = variable-size all-to-all.  DLBLAS_EP_MAX_TOKENS bounds the tokens per rank and call.
+        # With p2p a call can be cut into DLBLAS_EP_CHUNKS token chunks (default 1 = off) that run on their own
+        # streams with their own buffers, so that one chunk's pushes and barriers overlap the other chunk's GEMMs.
         backend = os.environ.get("DLBLAS_EP_BACKEND", "p2p" if ep_size > 1 else "nccl").lower()
         self.p2p_dispatcher = None
+        self.p2p_chunks = []
         if backend == "p2p" and ep_size > 1:
-            self.p2p_dispatcher = TokenDispatcherP2P(
-                ep_group, num_experts, self.num_local_experts, hidden_dim, out_dtype,
-                max_tokens_per_rank=int(os.environ.get("DLBLAS_EP_MAX_TOKENS", "8192")), max_top_k=top_k)
+            max_tokens = int(os.environ.get("DLBLAS_EP_MAX_TOKENS", "8192"))
+            chunks = max(1, int(os.environ.get("DLBLAS_EP_CHUNKS", "1")))
+            # fixed at construction from values every rank shares: all ranks must run the same sequence of
+            # pushes and barriers whatever their own token counts are
+            # ... and only where a chunk still brings about DLBLAS_EP_MIN_CHUNK_ROWS rows (default 1024) to every
+            # local expert: with fewer, badly filled GEMM tiles cost more than the overlap wins (measured at EP 2)
+            rows_per_expert = max_tokens * top_k // max(self.num_local_experts, 1) // chunks
+            if rows_per_expert < int(os.environ.get("DLBLAS_EP_MIN_CHUNK_ROWS", "1024")):
+                chunks = 1
+            per_chunk = (max_tokens + chunks - 1) // chunks
+            self.p2p_chunks = [TokenDispatcherP2P(ep_group, num_experts, self.num_local_experts, hidden_dim, out_dtype,
+                                                  max_tokens_per_rank=per_chunk, max_top_k=top_k)
+                               for _ in range(chunks)]
+            self.p2p_dispatcher = self.p2p_chunks[0]
+            self._chunk_streams = [torch.cuda.Stream() for _ in range(chunks - 1)]
+
+    def _p2p_experts(self, d, hs, topk_ids, topk_weights, up_weights, up_scale, down_weights, down_scale):
+        (rq, rs), rids, rw = d.dispatch_from_hidden(hs, topk_ids, topk_weights, self.block_size)
+        out_rows = moe_expert_forward(None, rq, rs, up_weights, up_scale, down_weights, down_scale, rw, rids,
+                                      topk_ids.shape[1], hs.dtype, 0, self.num_local_experts,
+                                      _C.QUANT_DIV_EPS, skip_unrouted_rows=True)
+        return d.combine(out_rows)
 
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,
                 up_weights: torch.Tensor, up_scale: torch.Tensor, down_weights: torch.Tensor,
@@ -57,13 +79,31 @@ class FusedMoENormal:
         if enable_moe_load_stats:
             FusedMoENormal.recorder.record(topk_ids, self.layer_index, self.num_experts)
         if self.p2p_dispatcher is not None:
-            d = self.p2p_dispatcher
             hs = hidden_states.flatten(0, -2) if hidden_states.dim() > 2 else hidden_states
-            (rq, rs), rids, rw = d.dispatch_from_hidden(hs, topk_ids, topk_weights, self.block_size)
-            out_rows = moe_expert_forward(None, rq, rs, up_weights, up_scale, down_weights, down_scale, rw, rids,
-                                          topk_ids.shape[1], hidden_states.dtype, 0, self.num_local_experts,
-                                          _C.QUANT_DIV_EPS, skip_unrouted_rows=True)
-            return d.combine(out_rows).view(hidden_states.shape)
+            t = hs.shape[0]
+            n = len(self.p2p_chunks)
+            assert t <= n * self.p2p_chunks[0].region_rows, "more tokens than DLBLAS_EP_MAX_TOKENS"
+            if n == 1:
+                out = self._p2p_experts(self.p2p_chunks[0], hs, topk_ids, topk_weights, up_weights, up_scale,
+                                        down_weights, down_scale)
+                return out.view(hidden_states.shape)
+            main = torch.cuda.current_stream()
+            step = min((t + n - 1) // n, self.p2p_chunks[0].region_rows) if t else 0
+            outs = []
+            for c in range(n):
+                sl = slice(c * step, min((c + 1) * step, t))
+                stream = main if c == 0 else self._chunk_streams[c - 1]
+                if c > 0:
+                    stream.wait_stream(main)
+                with torch.cuda.stream(stream):
+                    o = self._p2p_experts(self.p2p_chunks[c], hs[sl], topk_ids[sl].contiguous(),
+                                          topk_weights[sl].contiguous(), up_weights, up_scale, down_weights, down_scale)
+                    if c > 0:
+                        o.record_stream(main)
+                outs.append(o)
+            for st in self._chunk_streams:
+                main.wait_stream(st)
+            return torch.cat(outs, dim=0).view(hidden_states.shape)
         # per_token_group_quant_fp8 fused with the packing of the send buffer (one pass over the tokens)
         x, recv_topk_ids, recv_topk_weights, recv_tokens_per_expert = self.token_dispatcher.dispatch_from_hidden(
             hidden_states.flatten(0, -2) if hidden_states.dim() > 2 else hidden_states, topk_ids, topk_weights,

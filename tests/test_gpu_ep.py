@@ -42,10 +42,16 @@ def _worker(rank, world, port, ret):
         sl = slice(rank * nle, (rank + 1) * nle)
         local = [w13[sl].to(dev), w13s[sl].to(dev), w2[sl].to(dev), w2s[sl].to(dev)]
         os.environ["DLBLAS_EP_MAX_TOKENS"] = "256"
-        for backend, low_latency in (("p2p", False), ("nccl", False), ("nccl", True)):
+        for backend, low_latency in (("p2p", False), ("p2p-chunked", False), ("nccl", False), ("nccl", True)):
+            # two token chunks on two streams (ranks hold 96 and 128 tokens: chunks of 48 / 64)
+            os.environ["DLBLAS_EP_MIN_CHUNK_ROWS"] = "32" if backend == "p2p-chunked" else "1024"
+            os.environ["DLBLAS_EP_CHUNKS"] = "2" if backend == "p2p-chunked" else "1"
+            backend = backend.split("-")[0]
             os.environ["DLBLAS_EP_BACKEND"] = backend
             layer = build_deepep_moe(low_latency, world, dist.group.WORLD, e, h, 128, k, torch.bfloat16)
             assert (getattr(layer, "p2p_dispatcher", None) is not None) == (backend == "p2p")
+            if backend == "p2p":
+                assert len(layer.p2p_chunks) == (2 if os.environ["DLBLAS_EP_MIN_CHUNK_ROWS"] == "32" else 1)
             for _ in range(3):                      # repeated steps reuse the symmetric buffers
                 out = layer.forward(x.to(dev), ow.to(dev), oids.to(dev), *local)
             _C.check_status(dev)
