@@ -499,6 +499,69 @@ def run_profile(args):
     _C.check_status(dev)
 
 
+def run_decode(args):
+    """Optional second workload (not the headline line): the decode-shaped case of the benchmark set, 128
+    tokens per GPU with Zipf-skewed routing (alpha 1.2) through the low-latency (masked layout) layer and the
+    shared expert.  Prints per-step latency percentiles measured with one pair of CUDA events per step."""
+    import torch.distributed as dist
+
+    from dlblas_b200 import _C, ops
+    from dlblas_b200.layers.moe.ep_moe import FusedMoELowLatency
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    tokens = 128
+    nl = E // world
+    w13, w13s, w2, w2s = make_weights(nl + 1, 1000 + rank, dev)
+    layer = FusedMoELowLatency(world, group, E, H, layer_index=0)
+    g = torch.Generator().manual_seed(200 + rank)
+    x = torch.randn(tokens, H, generator=g).to(torch.bfloat16).to(dev)
+    pop = torch.randperm(E, generator=torch.Generator().manual_seed(77)).float() + 1.0
+    logits = (torch.randn(tokens, E, generator=g) + torch.log(pop ** -1.2 / (pop ** -1.2).sum())).to(dev)
+
+    def step():
+        w, ids = ops.route_softmax_topk(logits, TOPK, True)
+        routed = layer.forward(x, w, ids, w13[:nl], w13s[:nl], w2[:nl], w2s[:nl])
+        xq, xs = ops.quant_fp8(x, 128, _C.QUANT_RECIP_MUL, 0.0)
+        c1 = ops.fp8_gemm(xq, w13[nl], xs, w13s[nl], torch.bfloat16)
+        hq, hs = ops.silu_mul_quant(c1, _C.QUANT_RECIP_MUL)
+        return routed + ops.fp8_gemm(hq, w2[nl], hs, w2s[nl], torch.bfloat16)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in evs:
+        a.record()
+        step()
+        b.record()
+    torch.cuda.synchronize(dev)
+    _C.check_status(dev)
+    lat = torch.tensor([a.elapsed_time(b) for a, b in evs], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(lat, op=dist.ReduceOp.MAX)            # a step ends when its slowest rank ends
+    lat = lat.cpu().sort().values
+    if rank == 0:
+        p50 = float(lat[len(lat) // 2])
+        p99 = float(lat[min(len(lat) - 1, int(len(lat) * 0.99))])
+        print(json.dumps({"metric": "moe_decode_layer_latency_ms", "value": p50, "unit": "ms", "p50_ms": p50, "p99_ms": p99,
+                          "tokens_per_s": tokens * world / (p50 * 1e-3), "n_gpus": world, "steps": args.steps,
+                          "higher_is_better": False, "dtype": "fp8_e4m3", "data": "synthetic",
+                          "config": {"workload": "deepseek_v3_moe_decode", "tokens_per_gpu": tokens, "experts": E,
+                                     "top_k": TOPK, "routing": "softmax top-8, Zipf(1.2) expert popularity",
+                                     "parallelism": f"ep{world}", "exchange": "nccl all-to-all, masked layout"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile", default="", choices=["", "gemm1", "gemm2", "dense"],
@@ -511,9 +574,13 @@ def main():
     ap.add_argument("--tokens", type=int, default=T_PER_GPU, help="tokens per GPU per step")
     ap.add_argument("--cpu-tokens", type=int, default=32, help="tokens of the CPU baseline sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "decode"],
+                    help="prefill = the headline benchmark; decode = 128 tokens per GPU, latency percentiles")
     args = ap.parse_args()
     if args.profile:
         run_profile(args)
+    elif args.workload == "decode" and args.impl == "b200":
+        run_decode(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -329,6 +329,9 @@ class TokenDispatcherLowLatency:
         w_sz, nle, rpe = self.world_size, self.num_local_experts, self.rows_per_expert
         # pairs sorted by global expert = send order; the quantiser writes each token's row to its k slots
         _, _, _, pos, counts = ops.sort_by_expert(topk_idx, self.num_experts, want_pos=True, want_counts=True)
+        # slots without an expert (id -1) sort first and are not sent: shift the others down, drop those
+        unrouted = (pos < 0).sum().to(pos.dtype)
+        pos = torch.where(pos >= 0, pos - unrouted, torch.full_like(pos, -1))
         plan = make_low_latency_plan(counts, w_sz, self.rank, nle, self.group, rpe)
         plan.slot_pos, plan.num_tokens = pos, t
         send_x, send_s = ops.quant_fp8(hidden_states, 128, _C.QUANT_DIV_EPS, 1e-10, False, pos, k, plan.num_send)

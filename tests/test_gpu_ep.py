@@ -39,6 +39,10 @@ def _worker(rank, world, port, ret):
         logits = torch.randn(t, e, generator=g)
         ow, oids = O.softmax_topk(logits, k, True)
         ref = O.moe_layer(x, ow, oids, w13, w13s, w2, w2s, top_k=k)
+        ids_u = oids.clone()
+        ids_u[::3, 1] = -1
+        ids_u[5] = -1
+        ref_u = O.moe_layer(x, ow, ids_u, w13, w13s, w2, w2s, top_k=k)
         sl = slice(rank * nle, (rank + 1) * nle)
         local = [w13[sl].to(dev), w13s[sl].to(dev), w2[sl].to(dev), w2s[sl].to(dev)]
         os.environ["DLBLAS_EP_MAX_TOKENS"] = "256"
@@ -57,6 +61,11 @@ def _worker(rank, world, port, ret):
             _C.check_status(dev)
             err = O.rel_frobenius(out.cpu(), ref)
             assert out.shape == (t, h) and err < 2e-2, (backend, low_latency, err)
+            # slots without an expert (id -1) are dropped by every exchange
+            out_u = layer.forward(x.to(dev), ow.to(dev), ids_u.to(dev), *local)
+            _C.check_status(dev)
+            err_u = O.rel_frobenius(out_u.cpu(), ref_u)
+            assert err_u < 2e-2, (backend, low_latency, "unrouted slots", err_u)
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()

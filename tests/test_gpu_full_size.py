@@ -92,3 +92,33 @@ def test_fp16_layer_path():
     _C.check_status()
     ref = O.moe_layer(x, ow, oids, w13, w13s, w2, w2s, top_k=2)
     assert out.dtype == torch.float16 and O.rel_frobenius(out.cpu(), ref) < 2e-2
+
+
+def test_decode_shape_masked_layout_layer():
+    """Config 5 on one GPU: 128 tokens, 256 experts, top-8 with Zipf-skewed routing, through the low-latency
+    (masked layout) layer with a world of one; a sample of tokens against the oracle."""
+    from dlblas_b200 import _C, ops
+    from dlblas_b200.layers.moe.ep_moe import build_deepep_moe
+    t, h, inter, e, k = 128, 7168, 2048, 256, 8
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16)
+    ranks = torch.randperm(e, generator=g).float() + 1.0
+    logits = torch.randn(t, e, generator=g) + torch.log(ranks ** -1.2 / (ranks ** -1.2).sum())   # Zipf alpha = 1.2
+    w13, w13s, w2, w2s = _weights_on_device(e, inter, h, 2)
+    w, ids = ops.route_softmax_topk(logits.to(DEV), k, True)
+    ow, oids = O.softmax_topk(logits, k, True)
+    assert torch.equal(ids.cpu(), oids)
+    layer = build_deepep_moe(True, 1, None, e, h, 128, k, torch.bfloat16)
+    out = layer.forward(x.to(DEV), w, ids, w13, w13s, w2, w2s)
+    _C.check_status()
+    assert out.shape == (t, h)
+    rows = torch.tensor([0, 17, 64, 127])
+    hit = torch.unique(oids[rows])
+    # oracle on the sampled tokens, restricted to the experts they hit (renumbered), with the scale formula of
+    # the low-latency path's quantiser
+    remap = torch.full((e,), -1, dtype=torch.int64)
+    remap[hit] = torch.arange(hit.numel())
+    ref = O.fused_moe_v2(x[rows], w13[hit.to(DEV)].cpu(), w13s[hit.to(DEV)].cpu(), w2[hit.to(DEV)].cpu(),
+                         w2s[hit.to(DEV)].cpu(), ow[rows], remap[oids[rows]])
+    err = O.rel_frobenius(out.cpu()[rows], ref)
+    assert err < 2e-2, err
