@@ -250,6 +250,26 @@ class LowLatencyPlan:
         self.num_tokens = 0
 
 
+def make_single_rank_plan(counts: torch.Tensor, num_pairs: int, rows_per_expert: int) -> LowLatencyPlan:
+    """World of one: the plan stays on the device (no host round trip, so the layer can be captured in a CUDA
+    graph).  Buffers are sized for all `num_pairs` (token, slot) pairs; pairs without an expert sort to the
+    end of the send order and get destination -1."""
+    dev = counts.device
+    c = counts.to(torch.int64)
+    plan = LowLatencyPlan()
+    plan.num_send = plan.num_recv = num_pairs
+    plan.send_splits = plan.recv_splits = [num_pairs]
+    ends = torch.cumsum(c, 0)
+    rows = torch.arange(num_pairs, dtype=torch.int64, device=dev)
+    expert = torch.searchsorted(ends, rows, right=True)                  # expert of every sent row, E for the rest
+    valid = expert < c.numel()
+    e_safe = expert.clamp(max=c.numel() - 1)
+    within = rows - (ends - c)[e_safe]
+    plan.recv_dst = torch.where(valid, e_safe * rows_per_expert + within, torch.full_like(rows, -1)).to(torch.int32)
+    plan.masked_m = counts.to(torch.int32)
+    return plan
+
+
 def make_low_latency_plan(counts: torch.Tensor, world_size: int, rank: int, num_local_experts: int, group,
                           rows_per_expert: int) -> LowLatencyPlan:
     """counts: int32/int64 [E] number of (token, slot) pairs this rank routes to every global expert."""
@@ -272,13 +292,11 @@ def make_low_latency_plan(counts: torch.Tensor, world_size: int, rank: int, num_
     # received rows arrive grouped by source rank, inside a source sorted by local expert;
     # the masked layout wants, per expert, the rows of source 0 first, then source 1, ...
     before = torch.cumsum(local, dim=0) - local                                   # rows of earlier sources, per expert
-    dst = []
-    for s in range(world_size):
-        for j in range(num_local_experts):
-            c = int(local[s, j])
-            if c:
-                dst.append(torch.arange(c, dtype=torch.int32) + int(j * rows_per_expert + before[s, j]))
-    plan.recv_dst = (torch.cat(dst) if dst else torch.zeros(0, dtype=torch.int32)).to(dev)
+    seg_rows = local.reshape(-1)                                                  # arrival order: source-major, expert-minor
+    seg_base = (torch.arange(num_local_experts, dtype=torch.int64)[None, :] * rows_per_expert + before).reshape(-1)
+    seg_first = torch.cumsum(seg_rows, 0) - seg_rows
+    within = torch.arange(plan.num_recv, dtype=torch.int64) - torch.repeat_interleave(seg_first, seg_rows)
+    plan.recv_dst = (torch.repeat_interleave(seg_base, seg_rows) + within).to(torch.int32).to(dev)
     plan.masked_m = local.sum(dim=0).to(torch.int32).to(dev)
     assert int(plan.masked_m.max()) <= rows_per_expert if plan.masked_m.numel() else True, \
         "an expert received more rows than max_tokens_per_rank * world_size"
@@ -332,7 +350,10 @@ class TokenDispatcherLowLatency:
         # slots without an expert (id -1) sort first and are not sent: shift the others down, drop those
         unrouted = (pos < 0).sum().to(pos.dtype)
         pos = torch.where(pos >= 0, pos - unrouted, torch.full_like(pos, -1))
-        plan = make_low_latency_plan(counts, w_sz, self.rank, nle, self.group, rpe)
+        if w_sz == 1:
+            plan = make_single_rank_plan(counts, t * k, rpe)
+        else:
+            plan = make_low_latency_plan(counts, w_sz, self.rank, nle, self.group, rpe)
         plan.slot_pos, plan.num_tokens = pos, t
         send_x, send_s = ops.quant_fp8(hidden_states, 128, _C.QUANT_DIV_EPS, 1e-10, False, pos, k, plan.num_send)
         recv_x = torch.empty(plan.num_recv, h, dtype=torch.uint8, device=dev)
