@@ -54,8 +54,9 @@ SIGNATURES = {
                                    c_vp, c_vp, c_int, c_vp, c_vp, c_vp]),
     "dlb_p2p_unpack_meta": (c_int, [c_vp, c_int, c_int, c_vp, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
     "dlb_p2p_push_rows": (c_int, [c_vp, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
-    "dlb_grouped_gemm_16bit": (c_int, [c_vp, c_vp, c_int, c_i64, c_int, c_i64, c_i64, c_vp, c_int, c_vp, c_i64, c_vp,
-                                       c_vp]),
+    "dlb_grouped_gemm_16bit": (c_int, [c_vp, c_vp, c_int, c_i64, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_vp, c_i64,
+                                       c_vp, c_vp]),
+    "dlb_moe_build_tiles_rows": (c_int, [c_vp, c_vp, c_int, c_int, c_int, c_vp, c_int, c_vp]),
     "dlb_unpermute": (c_int, [c_vp, c_int, c_vp, c_vp, c_i64, c_int, c_i64, c_vp, c_vp]),
     "dlb_unpermute_bwd": (c_int, [c_vp, c_vp, c_int, c_vp, c_vp, c_i64, c_int, c_i64, c_vp, c_vp, c_vp]),
     "dlb_eplb_map_hash": (c_int, [c_vp, c_int, c_vp, c_vp, c_i64, c_int, c_int, c_int, ctypes.c_uint32, c_vp, c_vp]),

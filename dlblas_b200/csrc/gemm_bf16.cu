@@ -8,6 +8,14 @@
 //   warps 0-7  drain a finished accumulator (tcgen05.ld), round to the output type into a padded staging tile
 //   warps 10-11  send the staging rows out with one bulk copy each
 // While a tile is drained and stored the MMA warp already fills the other accumulator.  Waits are bounded.
+//
+// Two variants of the same kernel.  CTAS = 1: one CTA per 128 x 256 tile.  CTAS = 2: clusters of two CTAs
+// compute 256 x 256 tiles with tcgen05.mma.cta_group::2: each CTA loads its 128 rows of A and only half of the
+// B tile, the leader CTA issues the MMAs for both, and every CTA drains and stores its own 128 rows.  A single
+// CTA moves each operand byte through shared memory twice (TMA write, MMA read: 96 KB per 512 tensor-pipe
+// cycles, 1.5 x what the 128 B/clk port delivers); halving the B traffic lifts that bound (measured:
+// 1.12 -> 1.44 PFLOP/s on 8192 x 4096 x 7168).  The pair variant is used when the row groups are large enough
+// to fill 256-row tiles.  The pair's loads name no cluster-wide delivery: each CTA fetches its own half.
 #include "umma.cuh"
 
 namespace dlb {
@@ -16,9 +24,17 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int A_STAGE_BYTES = BM * UMMA_BK_BYTES;
-constexpr int B_STAGE_BYTES = BN * UMMA_BK_BYTES;
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int STAGES = 3;
+// per CTA: the whole B tile (CTAS = 1) or its half (CTAS = 2)
+template <int CTAS> struct Geo {
+  static constexpr int B_STAGE_BYTES = (BN / CTAS) * UMMA_BK_BYTES;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = CTAS == 1 ? 3 : 4;
+  static constexpr int STAGING_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = STAGING_OFF + BM * (BN * 2 + 16);
+  static constexpr int NUM_BARS = 2 * STAGES + 2 * 2 + 3;
+  static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
+  static constexpr int SMEM_BYTES = MISC_OFF + 16 + 1024;
+};
 constexpr int DRAIN_WARPS = 8;
 constexpr int PRODUCER_WARP = 8;
 constexpr int MMA_WARP = 9;
@@ -28,11 +44,6 @@ constexpr int NUM_THREADS = 384;
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_BUFS = 2;
 constexpr int STAGING_ROW_BYTES = BN * 2 + 16;
-constexpr int STAGING_OFF = STAGES * STAGE_BYTES;
-constexpr int BAR_OFF = STAGING_OFF + BM * STAGING_ROW_BYTES;
-constexpr int NUM_BARS = 2 * STAGES + 2 * TMEM_BUFS + 3;
-constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
-constexpr int SMEM_BYTES = MISC_OFF + 16 + 1024;
 
 struct Args16 {
   void* c;
@@ -46,8 +57,8 @@ struct Args16 {
 };
 
 // kind::f16: fp32 accumulate, A and B K-major, both of format `fmt` (0 = fp16, 1 = bf16), M = 128, N = BN
-constexpr uint32_t make_idesc16(uint32_t fmt) {
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t make_idesc16(uint32_t fmt, int ctas) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((ctas * BM) >> 4) << 24);
 }
 
 __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -60,10 +71,54 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
       : "memory");
 }
 
+// One instruction for the pair: M = 256 (128 rows from each CTA), B halves taken from both CTAs.
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load into this CTA's shared memory, completion counted on the barrier at `cluster_bar` (in the pair
+// leader's shared memory)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar)
+      : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair once all earlier MMAs have retired
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3)
+               : "memory");
+}
+
 struct Tile16 {
   int e, row0, rows, n0;
 };
-__device__ __forceinline__ Tile16 decode16(const Args16& g, int t) {
+template <int CTAS> __device__ __forceinline__ Tile16 decode16(const Args16& g, int t) {
   Tile16 ti;
   const int m_tile = t / g.num_n_tiles;
   const int n_tile = t - m_tile * g.num_n_tiles;
@@ -74,8 +129,8 @@ __device__ __forceinline__ Tile16 decode16(const Args16& g, int t) {
     ti.rows = v.z;
   } else {
     ti.e = 0;
-    ti.row0 = m_tile * BM;
-    ti.rows = min(BM, g.m - ti.row0);
+    ti.row0 = m_tile * CTAS * BM;
+    ti.rows = min(CTAS * BM, g.m - ti.row0);
   }
   ti.n0 = n_tile * BN;
   return ti;
@@ -91,13 +146,17 @@ template <> __device__ __forceinline__ uint32_t pack16<__half>(float a, float b)
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <typename T>
+template <typename T, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Args16 g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using G = Geo<CTAS>;
+  constexpr int STAGES = G::STAGES;
+  constexpr int STAGE_BYTES = G::STAGE_BYTES;
+  constexpr bool PAIR = CTAS == 2;
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar_base = smem_base + BAR_OFF;
+  const uint32_t bar_base = smem_base + G::BAR_OFF;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
@@ -105,12 +164,15 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 2 * TMEM_BUFS);
   const uint32_t staged_bar = drain_bar + 8u;
   const uint32_t sfree_bar = drain_bar + 16u;
-  uint8_t* staging = smem + STAGING_OFF;
-  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + MISC_OFF);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + MISC_OFF + 4);
+  uint8_t* staging = smem + G::STAGING_OFF;
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + G::MISC_OFF);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::MISC_OFF + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // 0 = leader of a pair: it issues the MMAs
+  const int worker = blockIdx.x / CTAS;                   // CTA or pair index
+  const int workers = gridDim.x / CTAS;
   const int kblocks = (g.k_bytes + UMMA_BK_BYTES - 1) / UMMA_BK_BYTES;
   const int num_m_tiles = g.tiles != nullptr ? __ldg(reinterpret_cast<const int*>(g.tiles)) : g.num_m_tiles_static;
   const int total_tiles = num_m_tiles * g.num_n_tiles;
@@ -123,7 +185,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
     for (int b = 0; b < TMEM_BUFS; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), DRAIN_WARPS);
+      mbar_init(tempty_bar(b), CTAS * DRAIN_WARPS);   // pair: the drain warps of both CTAs release the leader's
     }
     mbar_init(drain_bar, 1);
     mbar_init(staged_bar, DRAIN_WARPS);
@@ -134,22 +196,31 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == MMA_WARP) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(const_cast<uint32_t*>(tmem_holder))),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(const_cast<uint32_t*>(tmem_holder))),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(const_cast<uint32_t*>(tmem_holder))),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();   // both CTAs' barriers exist before anything remote touches them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == PRODUCER_WARP) {
     uint32_t it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const Tile16 ti = decode16(g, t);
+    for (int t = worker; t < total_tiles && ok; t += workers) {
+      const Tile16 ti = decode16<CTAS>(g, t);
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
         const int s = it % STAGES;
         if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, abort_flag, limit)) {
@@ -158,7 +229,14 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         }
         const uint32_t a_dst = smem_base + s * STAGE_BYTES;
         const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-        if (elect_one()) {
+        if constexpr (PAIR) {
+          const uint32_t lead_full = mapa(full_bar(s), 0);
+          if (elect_one()) {
+            if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);      // the loads of both CTAs
+            tma_load_2d_pair(a_dst, &tmap_a, kb * UMMA_BK_BYTES, ti.row0 + (int)rank * BM, lead_full);
+            tma_load_2d_pair(b_dst, &tmap_b, kb * UMMA_BK_BYTES, ti.e * g.n + ti.n0 + (int)rank * (BN / 2), lead_full);
+          }
+        } else if (elect_one()) {
           mbar_expect_tx(full_bar(s), STAGE_BYTES);
           tma_load_2d(a_dst, &tmap_a, kb * UMMA_BK_BYTES, ti.row0, full_bar(s));
           tma_load_2d(b_dst, &tmap_b, kb * UMMA_BK_BYTES, ti.e * g.n + ti.n0, full_bar(s));
@@ -175,7 +253,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   } else if (warp == MMA_WARP) {
     uint32_t it = 0, tile_no = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
+    for (int t = worker; t < total_tiles && ok && rank == 0; t += workers, ++tile_no) {
       const int b = tile_no % TMEM_BUFS;
       if (!mbar_wait(tempty_bar(b), ((tile_no / TMEM_BUFS) & 1u) ^ 1u, abort_flag, limit)) {
         ok = false;
@@ -193,17 +271,31 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         const uint64_t a_desc = make_smem_desc(a_addr);
         const uint64_t b_desc = make_smem_desc(a_addr + A_STAGE_BYTES);
         if (elect_one()) {
+          if constexpr (PAIR) {
 #pragma unroll
-          for (int kk = 0; kk < UMMA_BK_BYTES / 32; ++kk)
-            tc_mma_f16(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(empty_bar(s));
-          if (kb == kblocks - 1) tc_commit(tfull_bar(b));
+            for (int kk = 0; kk < UMMA_BK_BYTES / 32; ++kk)
+              tc_mma_f16_pair(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            tc_commit_pair(empty_bar(s));                          // frees the stage in both CTAs
+            if (kb == kblocks - 1) tc_commit_pair(tfull_bar(b));   // both CTAs' drain warps
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < UMMA_BK_BYTES / 32; ++kk)
+              tc_mma_f16(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            tc_commit(empty_bar(s));
+            if (kb == kblocks - 1) tc_commit(tfull_bar(b));
+          }
         }
         __syncwarp();
       }
     }
     if (!ok) {
-      if (elect_one()) tc_commit(drain_bar);
+      if (elect_one()) {
+        if constexpr (PAIR)
+          asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(drain_bar)
+                       : "memory");
+        else
+          tc_commit(drain_bar);
+      }
       __syncwarp();
       mbar_wait(drain_bar, 0, abort_flag + 1, 40000000ull);
     }
@@ -211,18 +303,20 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const int ew = warp - STORE_WARP0;
     uint32_t tile_no = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
-      const Tile16 ti = decode16(g, t);
+    for (int t = worker; t < total_tiles && ok; t += workers, ++tile_no) {
+      const Tile16 ti = decode16<CTAS>(g, t);
       if (!mbar_wait(staged_bar, tile_no & 1u, abort_flag, limit)) {
         ok = false;
         break;
       }
       const uint32_t bytes = (uint32_t)min(BN, g.n - ti.n0) * 2u;
+      const int my_row0 = ti.row0 + (int)rank * BM;               // this CTA's 128 rows of the tile
+      const int my_rows = min(BM, max(0, ti.rows - (int)rank * BM));
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         const int row = ew * 64 + i * 32 + lane;
-        if (row < ti.rows)
-          bulk_store(reinterpret_cast<T*>(g.c) + ((long long)ti.row0 + row) * g.ldc + ti.n0,
+        if (row < my_rows)
+          bulk_store(reinterpret_cast<T*>(g.c) + ((long long)my_row0 + row) * g.ldc + ti.n0,
                      smem_u32(staging + row * STAGING_ROW_BYTES), bytes);
       }
       bulk_commit();
@@ -240,7 +334,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint8_t* srow = staging + r * STAGING_ROW_BYTES + wg * 128 * 2;
     uint32_t tile_no = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
+    for (int t = worker; t < total_tiles && ok; t += workers, ++tile_no) {
       const int b = tile_no % TMEM_BUFS;
       if (!mbar_wait(tfull_bar(b), (tile_no / TMEM_BUFS) & 1u, abort_flag, limit) ||
           !mbar_wait(sfree_bar, (tile_no & 1u) ^ 1u, abort_flag, limit)) {
@@ -259,7 +353,10 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           // the whole accumulator is in registers: the MMA warp may reuse it
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(tempty_bar(b));
+          if (lane == 0) {
+            if (rank == 0) mbar_arrive(tempty_bar(b));
+            else mbar_arrive_cluster(mapa(tempty_bar(b), 0));
+          }
         }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -287,17 +384,22 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();   // no CTA leaves while its partner may still signal its barriers
   if (threadIdx.x == 0 && *abort_flag != 0 && g.status != nullptr) atomicExch(g.status, DLB_STATUS_TIMEOUT);
   if (warp == MMA_WARP) {
     __syncwarp();
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
-template <typename T>
+template <typename T, int CTAS>
 int launch16(const CUtensorMap& ma, const CUtensorMap& mb, const Args16& g, int grid, cudaStream_t st) {
-  auto kern = gemm16_kernel<T>;
+  auto kern = gemm16_kernel<T, CTAS>;
+  constexpr int SMEM_BYTES = Geo<CTAS>::SMEM_BYTES;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -307,9 +409,26 @@ int launch16(const CUtensorMap& ma, const CUtensorMap& mb, const Args16& g, int 
     if (rc != DLB_OK) return rc;
     configured[dev] = true;
   }
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, g);
+  if constexpr (CTAS == 1) {
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, g);
+    DLB_CHECK_LAUNCH("gemm16_kernel");
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int rc = check_cuda(cudaLaunchKernelEx(&cfg, kern, ma, mb, g), "cudaLaunchKernelEx(gemm16_kernel, pairs)");
+    if (rc != DLB_OK) return rc;
+  }
   count_launch();
-  DLB_CHECK_LAUNCH("gemm16_kernel");
   return DLB_OK;
 }
 
@@ -319,8 +438,8 @@ int launch16(const CUtensorMap& ma, const CUtensorMap& mb, const Args16& g, int 
 using namespace dlb;
 
 extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t rows, int num_groups, int64_t n,
-                                      int64_t k, const int32_t* tiles, int max_tiles, void* c, int64_t ldc,
-                                      int32_t* status, void* stream) {
+                                      int64_t k, const int32_t* tiles, int max_tiles, int tile_rows, void* c,
+                                      int64_t ldc, int32_t* status, void* stream) {
   DLB_REQUIRE(rows >= 0 && n > 0 && k > 0 && num_groups > 0, DLB_ERR_INVALID,
               "grouped_gemm_16bit: bad sizes rows=%lld n=%lld k=%lld groups=%d", (long long)rows, (long long)n,
               (long long)k, num_groups);
@@ -331,6 +450,7 @@ extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, i
   DLB_REQUIRE(rows < (1ll << 31) && (long long)num_groups * n < (1ll << 31) && 2 * k < (1ll << 31), DLB_ERR_INVALID,
               "grouped_gemm_16bit: size too large");
   DLB_REQUIRE(tiles != nullptr || num_groups == 1, DLB_ERR_INVALID, "grouped_gemm_16bit: several groups need a tile list");
+  DLB_REQUIRE(tile_rows == 128 || tile_rows == 256, DLB_ERR_INVALID, "grouped_gemm_16bit: tile_rows must be 128 or 256");
   if (rows == 0 || (tiles != nullptr && max_tiles == 0)) return DLB_OK;
   DLB_REQUIRE(a && b && c, DLB_ERR_INVALID, "grouped_gemm_16bit: null pointer");
   DLB_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 16 == 0) &&
@@ -348,15 +468,20 @@ extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, i
   g.m = (int)rows;
   g.n = (int)n;
   g.k_bytes = (int)(2 * k);
-  g.num_m_tiles_static = (int)ceil_div(rows, (int64_t)BM);
+  const int ctas = tile_rows / BM;
+  g.num_m_tiles_static = (int)ceil_div(rows, (int64_t)tile_rows);
   g.num_n_tiles = (int)ceil_div(n, (int64_t)BN);
-  g.idesc = make_idesc16(dtype == DLB_BF16 ? 1u : 0u);
+  g.idesc = make_idesc16(dtype == DLB_BF16 ? 1u : 0u, ctas);
   g.status = status;
   g.timeout_cycles = DEFAULT_TIMEOUT_CYCLES;
-  const int sms = sm_count();
+  const int workers = sm_count() / ctas;
   const long long total = (long long)(tiles != nullptr ? max_tiles : g.num_m_tiles_static) * g.num_n_tiles;
-  const int grid = (int)(total < sms ? total : sms);
+  const int grid = ctas * (int)(total < workers ? total : workers);
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == DLB_BF16) return launch16<__nv_bfloat16>(ma, mb, g, grid, st);
-  return launch16<__half>(ma, mb, g, grid, st);
+  if (ctas == 2) {
+    if (dtype == DLB_BF16) return launch16<__nv_bfloat16, 2>(ma, mb, g, grid, st);
+    return launch16<__half, 2>(ma, mb, g, grid, st);
+  }
+  if (dtype == DLB_BF16) return launch16<__nv_bfloat16, 1>(ma, mb, g, grid, st);
+  return launch16<__half, 1>(ma, mb, g, grid, st);
 }

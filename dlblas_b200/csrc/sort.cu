@@ -293,7 +293,8 @@ int run_sort(const IdT* ids, long long n, int num_experts, const SortOut& o, voi
 // tiles[0] = {num_tiles, 0, 0, 0}; tiles[1 + i] = {expert, first row, valid rows, 0}.
 __global__ void __launch_bounds__(1024) build_tiles_kernel(const long long* exp_start, const long long* exp_end,
                                                            const int* masked_m, int expert_offset, int num_local,
-                                                           int rows_per_expert, int4* tiles, int max_tiles) {
+                                                           int rows_per_expert, int tile_rows, int4* tiles,
+                                                           int max_tiles) {
   __shared__ int warp_sums[32];
   __shared__ int carry_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -313,7 +314,7 @@ __global__ void __launch_bounds__(1024) build_tiles_kernel(const long long* exp_
         if (rows < 0) rows = 0;
       }
     }
-    const int nt = (rows + 127) / 128;
+    const int nt = (rows + tile_rows - 1) / tile_rows;
     int inc = nt;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -328,7 +329,8 @@ __global__ void __launch_bounds__(1024) build_tiles_kernel(const long long* exp_
     const int first = carry + woff + inc - nt;
     for (int i = 0; i < nt; ++i) {
       const int idx = first + i;
-      if (idx < max_tiles) tiles[1 + idx] = make_int4(e, (int)(start + (long long)i * 128), min(128, rows - i * 128), 0);
+      if (idx < max_tiles)
+        tiles[1 + idx] = make_int4(e, (int)(start + (long long)i * tile_rows), min(tile_rows, rows - i * tile_rows), 0);
     }
     __syncthreads();
     if (threadIdx.x == blockDim.x - 1) carry_s = carry + woff + inc;
@@ -440,7 +442,24 @@ extern "C" int dlb_moe_build_tiles(const int64_t* exp_start, const int64_t* exp_
   DLB_REQUIRE((uintptr_t)tiles % 16 == 0, DLB_ERR_INVALID, "build_tiles: tiles must be 16-byte aligned");
   build_tiles_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(reinterpret_cast<const long long*>(exp_start),
                                                            reinterpret_cast<const long long*>(exp_end), nullptr,
-                                                           expert_offset, num_local_experts, 0,
+                                                           expert_offset, num_local_experts, 0, 128,
+                                                           reinterpret_cast<int4*>(tiles), max_tiles);
+  count_launch();
+  DLB_CHECK_LAUNCH("build_tiles_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_moe_build_tiles_rows(const int64_t* exp_start, const int64_t* exp_end, int expert_offset,
+                                        int num_local_experts, int tile_rows, int32_t* tiles, int max_tiles,
+                                        void* stream) {
+  DLB_REQUIRE(exp_start && exp_end && tiles, DLB_ERR_INVALID, "build_tiles_rows: null pointer");
+  DLB_REQUIRE(num_local_experts > 0 && expert_offset >= 0 && max_tiles >= 0, DLB_ERR_INVALID,
+              "build_tiles_rows: bad sizes");
+  DLB_REQUIRE(tile_rows == 128 || tile_rows == 256, DLB_ERR_INVALID, "build_tiles_rows: tile_rows must be 128 or 256");
+  DLB_REQUIRE((uintptr_t)tiles % 16 == 0, DLB_ERR_INVALID, "build_tiles_rows: tiles must be 16-byte aligned");
+  build_tiles_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(reinterpret_cast<const long long*>(exp_start),
+                                                           reinterpret_cast<const long long*>(exp_end), nullptr,
+                                                           expert_offset, num_local_experts, 0, tile_rows,
                                                            reinterpret_cast<int4*>(tiles), max_tiles);
   count_launch();
   DLB_CHECK_LAUNCH("build_tiles_kernel");
@@ -454,7 +473,8 @@ extern "C" int dlb_moe_build_tiles_masked(const int32_t* masked_m, int num_local
               "build_tiles_masked: bad sizes");
   DLB_REQUIRE((uintptr_t)tiles % 16 == 0, DLB_ERR_INVALID, "build_tiles_masked: tiles must be 16-byte aligned");
   build_tiles_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(nullptr, nullptr, masked_m, 0, num_local_experts,
-                                                           rows_per_expert, reinterpret_cast<int4*>(tiles), max_tiles);
+                                                           rows_per_expert, 128, reinterpret_cast<int4*>(tiles),
+                                                           max_tiles);
   count_launch();
   DLB_CHECK_LAUNCH("build_tiles_kernel");
   return DLB_OK;

@@ -4,6 +4,8 @@ C[rows of group g] = A[rows of g] @ B[g] for contiguous row groups of sizes `siz
 The tcgen05 kernel wants both operands K-major, i.e. B as [G, N, K] (`trans_b=True`); with `trans_b=False`
 (B [G, K, N]) the weights are transposed once per call, an extra pass over B.  Tile list and group offsets are
 built on the device; nothing synchronises with the host."""
+import os
+
 import torch
 from torch import Tensor
 
@@ -32,8 +34,13 @@ def m_grouped_gemm(A: Tensor, B: Tensor, size_per_group: torch.Tensor, trans_b: 
         return C
     ends = torch.cumsum(size_per_group.to(torch.int64), 0)
     starts = ends - size_per_group.to(torch.int64)
-    max_tiles = M // 128 + num_groups
-    tiles = ops.build_tiles(starts, ends, 0, num_groups, max_tiles)
+    # pairs of CTAs on 256-row tiles when the groups are large enough to fill them (decided from the shapes,
+    # no look at the group sizes on the host); DLBLAS_GEMM16_TILE_ROWS = 128 / 256 overrides
+    tile_rows = int(os.environ.get("DLBLAS_GEMM16_TILE_ROWS", "256" if M >= 512 * num_groups else "128"))
+    max_tiles = M // tile_rows + num_groups
+    tiles = torch.empty((max_tiles + 1) * 4, dtype=torch.int32, device=A.device)
+    check(lib().dlb_moe_build_tiles_rows(ptr(starts), ptr(ends), 0, num_groups, tile_rows, ptr(tiles), max_tiles,
+                                         stream(A.device)))
     check(lib().dlb_grouped_gemm_16bit(ptr(A), ptr(Bt), dtype_code(A.dtype), M, num_groups, N, K, ptr(tiles), max_tiles,
-                                       ptr(C), N, ptr(status_word(A.device)), stream(A.device)))
+                                       tile_rows, ptr(C), N, ptr(status_word(A.device)), stream(A.device)))
     return C

@@ -106,6 +106,9 @@ DLB_API int dlb_sort_by_expert_static(const void* ids, int ids_dtype, int64_t nu
  * (masked layout [E, rows_per_expert, K] of FusedMoELowLatency, dlblas/layers/moe/ep_moe.py:199-261). */
 DLB_API int dlb_moe_build_tiles(const int64_t* exp_start, const int64_t* exp_end, int expert_offset,
                         int num_local_experts, int32_t* tiles, int max_tiles, void* stream);
+/* Same list with tiles of `tile_rows` rows (128 or 256). */
+DLB_API int dlb_moe_build_tiles_rows(const int64_t* exp_start, const int64_t* exp_end, int expert_offset,
+                             int num_local_experts, int tile_rows, int32_t* tiles, int max_tiles, void* stream);
 DLB_API int dlb_moe_build_tiles_masked(const int32_t* masked_m, int num_local_experts, int rows_per_expert,
                                int32_t* tiles, int max_tiles, void* stream);
 
@@ -219,11 +222,13 @@ DLB_API int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32_t*
 /* ---- 16-bit grouped GEMM -----------------------------------------------------------------
  * m_grouped_gemm with trans_b = True (dlblas/kernels/grouped_gemm/BF16/m_grouped_gemm.py:235-352):
  * c[row, :] = a[row, :] * b[g]^T for the rows of group g; a [rows, k] and b [num_groups, n, k] bf16 or fp16,
- * K-major; c [rows, ldc] of the same type, fp32 accumulation.  `tiles` is the tile list of
- * dlb_moe_build_tiles over the groups' row ranges (NULL: one group, dense).  k, n, ldc multiples of 8. */
+ * K-major; c [rows, ldc] of the same type, fp32 accumulation.  `tiles` is a tile list over the groups' row ranges
+ * built by dlb_moe_build_tiles_rows with the same `tile_rows` (NULL: one group, dense).  tile_rows = 128: one
+ * CTA per tile; 256: pairs of CTAs on 256-row tiles (tcgen05 cta_group::2), the faster choice when groups hold
+ * several hundred rows.  k, n, ldc multiples of 8. */
 DLB_API int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t rows, int num_groups, int64_t n,
-                           int64_t k, const int32_t* tiles, int max_tiles, void* c, int64_t ldc, int32_t* status,
-                           void* stream);
+                           int64_t k, const int32_t* tiles, int max_tiles, int tile_rows, void* c, int64_t ldc,
+                           int32_t* status, void* stream);
 
 /* ---- training-side permutation (dlblas/kernels/permute/moe_triton_kernels.py) ------------------
  * row_id_map int32 [top_k * tokens], k-major: destination row of (token, slot) in the permuted tensor, -1 for

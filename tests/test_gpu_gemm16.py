@@ -10,7 +10,9 @@ DEV = "cuda"
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("trans_b", [True, False])
-def test_m_grouped_gemm(dtype, trans_b):
+@pytest.mark.parametrize("tile_rows", [128, 256])      # one CTA per tile / pairs of CTAs (cta_group::2)
+def test_m_grouped_gemm(dtype, trans_b, tile_rows, monkeypatch):
+    monkeypatch.setenv("DLBLAS_GEMM16_TILE_ROWS", str(tile_rows))
     from dlblas_b200 import _C
     from dlblas_b200.kernels.grouped_gemm.BF16 import m_grouped_gemm
     g = torch.Generator().manual_seed(13)
@@ -35,9 +37,17 @@ def test_m_grouped_gemm_large_and_empty():
     sizes = torch.tensor([1000, 3000, 17, 4175], device=DEV)
     a = torch.randn(8192, 2048, generator=g, device=DEV, dtype=torch.bfloat16)
     b = torch.randn(4, 1024, 2048, generator=g, device=DEV, dtype=torch.bfloat16) * 0.05
-    out = m_grouped_gemm(a, b, sizes, trans_b=True)
-    _C.check_status()
     ref = utils.gmm(a.float(), b.float(), sizes.cpu(), trans_b=True)
+    out = m_grouped_gemm(a, b, sizes, trans_b=True)              # 2048 rows per group on average: the pair kernel
+    _C.check_status()
     assert float((out.float() - ref).norm() / ref.norm()) < 3e-3
+    import os
+    os.environ["DLBLAS_GEMM16_TILE_ROWS"] = "128"
+    try:
+        out1 = m_grouped_gemm(a, b, sizes, trans_b=True)
+    finally:
+        del os.environ["DLBLAS_GEMM16_TILE_ROWS"]
+    _C.check_status()
+    assert torch.equal(out, out1)                                # same sums in the same order
     empty = m_grouped_gemm(a[:0], b, torch.zeros(4, dtype=torch.int64, device=DEV), trans_b=True)
     assert empty.shape == (0, 1024)
