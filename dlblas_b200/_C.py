@@ -41,8 +41,8 @@ SIGNATURES = {
     "dlb_permute_rows": (c_int, [c_vp, c_i64, c_vp, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_vp]),
     "dlb_silu_and_mul": (c_int, [c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_i64, c_vp]),
     "dlb_silu_mul_quant": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_f, c_int, c_vp, c_i64, c_vp, c_vp, c_vp]),
-    "dlb_fp8_gemm": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp]),
-    "dlb_moe_grouped_gemm": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_vp,
+    "dlb_fp8_gemm": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_int, c_vp, c_vp]),
+    "dlb_moe_grouped_gemm": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_int, c_vp,
                                      c_int, c_i64, c_vp, c_int, c_f, c_vp, c_vp, c_vp, c_vp]),
     "dlb_ep_dest_ranks": (c_int, [c_vp, c_int, c_i64, c_int, c_int, c_int, c_vp, c_vp]),
     "dlb_moe_sum_topk": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_vp, c_int, c_i64, c_i64, c_int, c_vp, c_vp]),

@@ -73,14 +73,15 @@ struct GemmArgs {
 };
 
 // kind::f8f6f4, A and B e4m3 K-major, fp32 accumulate, M = 128, N = bn.
-__host__ __device__ constexpr uint32_t make_idesc(int bn) {
-  return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc(int bn, int ctas = 1) {
+  return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((ctas * BM) >> 4) << 24);
 }
 
-template <int BN> struct Cfg {
-  static constexpr int B_STAGE_BYTES = BN * BK;
+// CTAS = 2: pairs of CTAs on 256-row tiles (tcgen05 cta_group::2); every CTA then stages only half of the B tile
+template <int BN, int CTAS = 1> struct Cfg {
+  static constexpr int B_STAGE_BYTES = (BN / CTAS) * BK;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 3 : 5;
+  static constexpr int STAGES = (BN == 256) ? (CTAS == 2 ? 4 : 3) : 5;
   static constexpr int TMEM_BUFS = TMEM_COLS / BN;
   static constexpr int SEG = BN / 4;  // columns per thread segment (two segments per thread)
   // Staging tile of the epilogue: BM rows of BN 16-bit values.  Rows are padded by 16 bytes so
@@ -100,8 +101,10 @@ struct Tile {
   int e, row0, rows, n0;
 };
 
-template <int BN, int MODE>
-__device__ __forceinline__ Tile decode_tile(const GemmArgs& g, int t) {
+// The part of tile t that CTA `rank` of a pair works on (CTAS = 2: rows [rank * 128, rank * 128 + 128) of the
+// 256-row tile; its `rows` is 0 when the tile ends before them).
+template <int BN, int MODE, int CTAS = 1>
+__device__ __forceinline__ Tile decode_tile(const GemmArgs& g, int t, int rank = 0) {
   Tile ti;
   const int m_tile = t / g.num_n_tiles;
   const int n_tile = t - m_tile * g.num_n_tiles;
@@ -112,8 +115,12 @@ __device__ __forceinline__ Tile decode_tile(const GemmArgs& g, int t) {
     ti.rows = v.z;
   } else {
     ti.e = 0;
-    ti.row0 = m_tile * BM;
-    ti.rows = min(BM, g.m - ti.row0);
+    ti.row0 = m_tile * CTAS * BM;
+    ti.rows = min(CTAS * BM, g.m - ti.row0);
+  }
+  if constexpr (CTAS == 2) {
+    ti.row0 += rank * BM;
+    ti.rows = min(BM, max(0, ti.rows - rank * BM));
   }
   ti.n0 = n_tile * (MODE == DLB_EPI_SWIGLU_QUANT ? BN / 2 : BN);
   return ti;
@@ -159,11 +166,12 @@ __device__ __forceinline__ void store_row(OutT* dst, const float (&acc)[NCOLS], 
   }
 }
 
-template <int BN, int MODE, typename OutT>
+template <int BN, int MODE, typename OutT, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const GemmArgs g) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CTAS>;
+  constexpr bool PAIR = CTAS == 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
@@ -182,6 +190,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // 0 = leader of a pair: it issues the MMAs
+  const int worker = blockIdx.x / CTAS;                   // CTA or pair index
+  const int workers = gridDim.x / CTAS;
   const int kblocks = g.k / BK;
   const int num_m_tiles = g.tiles != nullptr ? __ldg(reinterpret_cast<const int*>(g.tiles)) : g.num_m_tiles_static;
   const int total_tiles = num_m_tiles * g.num_n_tiles;
@@ -194,7 +205,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     for (int b = 0; b < C::TMEM_BUFS; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), EPI_WARPS);
+      mbar_init(tempty_bar(b), CTAS * EPI_WARPS);   // pair: the promotion warps of both CTAs release the leader's
     }
     mbar_init(drain_bar, 1);
     mbar_init(staged_bar, EPI_WARPS);
@@ -205,14 +216,23 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == MMA_WARP) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(const_cast<uint32_t*>(tmem_holder))),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(const_cast<uint32_t*>(tmem_holder))),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(const_cast<uint32_t*>(tmem_holder))),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();   // both CTAs' barriers exist before anything remote touches them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -228,8 +248,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const Tile ti = decode_tile<BN, MODE>(g, t);
+      for (int t = worker; t < total_tiles && ok; t += workers) {
+        const Tile ti = decode_tile<BN, MODE, CTAS>(g, t, (int)rank);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
@@ -239,7 +259,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-          if (elect_one()) {
+          if constexpr (PAIR) {
+            // each CTA fetches its 128 rows of A and its half of the B tile (the gate slab in the leader, the up
+            // slab in its partner for the fused w13 epilogue); all of it is counted on the leader's barrier
+            const uint32_t lead_full = mapa(full_bar(s), 0);
+            if (elect_one()) {
+              if (rank == 0) mbar_expect_tx(full_bar(s), 2 * C::STAGE_BYTES);
+              tma_load_2d_pair(a_dst, &tmap_a, kb * BK, ti.row0, lead_full);
+              const int b_row = (MODE == DLB_EPI_SWIGLU_QUANT) ? ti.e * g.n + (int)rank * g.n_half + ti.n0
+                                                                : ti.e * g.n + ti.n0 + (int)rank * (BN / 2);
+              tma_load_2d_pair(b_dst, &tmap_b, kb * BK, b_row, lead_full);
+            }
+          } else if (elect_one()) {
             mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
             tma_load_2d(a_dst, &tmap_a, kb * BK, ti.row0, full_bar(s));
             if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
@@ -264,10 +295,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
   } else if (warp == MMA_WARP) {
     {
-      constexpr uint32_t idesc = make_idesc(BN);
+      constexpr uint32_t idesc = make_idesc(BN, CTAS);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = worker; t < total_tiles && ok && rank == 0; t += workers) {
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % C::STAGES;
           const int b = it % C::TMEM_BUFS;
@@ -282,19 +313,33 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const uint64_t b_desc = make_smem_desc(a_addr + A_STAGE_BYTES);
           const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
           if (elect_one()) {
+            if constexpr (PAIR) {
 #pragma unroll
-            for (int kk = 0; kk < BK / 32; ++kk) {
-              // +32 bytes along K inside the 128 B swizzle row == +2 in the (addr >> 4) field
-              tc_mma_f8(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, kk > 0 ? 1u : 0u);
+              for (int kk = 0; kk < BK / 32; ++kk)
+                tc_mma_f8_pair(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, kk > 0 ? 1u : 0u);
+              tc_commit_pair(empty_bar(s));   // both CTAs' stages
+              tc_commit_pair(tfull_bar(b));   // both CTAs' promotion warps
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < BK / 32; ++kk) {
+                // +32 bytes along K inside the 128 B swizzle row == +2 in the (addr >> 4) field
+                tc_mma_f8(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, kk > 0 ? 1u : 0u);
+              }
+              tc_commit(empty_bar(s));   // smem stage reusable once these MMAs retire
+              tc_commit(tfull_bar(b));   // accumulator ready for the promotion warps
             }
-            tc_commit(empty_bar(s));   // smem stage reusable once these MMAs retire
-            tc_commit(tfull_bar(b));   // accumulator ready for the promotion warps
           }
           __syncwarp();
         }
       }
       if (!ok) {
-        if (elect_one()) tc_commit(drain_bar);
+        if (elect_one()) {
+          if constexpr (PAIR)
+            asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(drain_bar)
+                         : "memory");
+          else
+            tc_commit(drain_bar);
+        }
         __syncwarp();
         mbar_wait(drain_bar, 0, abort_flag + 1, 40000000ull);
       }
@@ -304,8 +349,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     const int ew = warp - STORE_WARP0;
     uint32_t tile_no = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
-      const Tile ti = decode_tile<BN, MODE>(g, t);
+    for (int t = worker; t < total_tiles && ok; t += workers, ++tile_no) {
+      const Tile ti = decode_tile<BN, MODE, CTAS>(g, t, (int)rank);
       if constexpr (MODE == DLB_EPI_SWIGLU_QUANT) {
         // A staging row holds the tile's 128 gate columns, then its 128 up columns, already
         // rounded to OutT.  Reference rounding points: silu(gate)*up -> OutT, then
@@ -402,8 +447,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     uint32_t it = 0;
     uint32_t tile_no = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
-      const Tile ti = decode_tile<BN, MODE>(g, t);
+    for (int t = worker; t < total_tiles && ok; t += workers, ++tile_no) {
+      const Tile ti = decode_tile<BN, MODE, CTAS>(g, t, (int)rank);
       const bool row_ok = r < ti.rows;
       const long long p = (long long)ti.row0 + r;          // row of A / sorted position
       const float* as_ptr = g.a_s + (row_ok ? p : (long long)ti.row0) * g.a_s_rs;
@@ -489,7 +534,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             // every column of this accumulator is in registers: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(b));
+            if (lane == 0) {
+              if (rank == 0) mbar_arrive(tempty_bar(b));
+              else mbar_arrive_cluster(mapa(tempty_bar(b), 0));
+            }
           }
           {
             const uint64_t sc = ((2 * q) * 32 < SEG) ? sc0 : sc1;
@@ -578,35 +626,63 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   // ---- teardown ----------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();   // no CTA leaves while its partner may still signal its barriers
   if (threadIdx.x == 0 && *abort_flag != 0 && g.status != nullptr) atomicExch(g.status, DLB_STATUS_TIMEOUT);
   if (warp == MMA_WARP) {
     __syncwarp();
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
-template <int BN, int MODE, typename OutT>
+template <int BN, int MODE, typename OutT, int CTAS = 1>
 int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int grid, cudaStream_t st) {
-  auto kern = gemm_fp8_kernel<BN, MODE, OutT>;
+  auto kern = gemm_fp8_kernel<BN, MODE, OutT, CTAS>;
+  constexpr int SMEM = Cfg<BN, CTAS>::SMEM_BYTES;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES),
+    int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM),
                         "cudaFuncSetAttribute(gemm_fp8_kernel)");
     if (rc != DLB_OK) return rc;
     configured[dev] = true;
   }
-  kern<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(ma, mb, g);
+  if constexpr (CTAS == 1) {
+    kern<<<grid, NUM_THREADS, SMEM, st>>>(ma, mb, g);
+    DLB_CHECK_LAUNCH("gemm_fp8_kernel");
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int rc = check_cuda(cudaLaunchKernelEx(&cfg, kern, ma, mb, g), "cudaLaunchKernelEx(gemm_fp8_kernel, pairs)");
+    if (rc != DLB_OK) return rc;
+  }
   count_launch();
-  DLB_CHECK_LAUNCH("gemm_fp8_kernel");
   return DLB_OK;
 }
 
 template <int MODE>
-int launch_typed(int bn, int c_dtype, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int grid,
-                 cudaStream_t st) {
+int launch_typed(int bn, int ctas, int c_dtype, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g,
+                 int grid, cudaStream_t st) {
+  if (ctas == 2) {
+    // pairs exist for 256-wide tiles with a 16-bit output (the ones that go through the staging tile)
+    if (bn == 256 && c_dtype == DLB_BF16) return launch_one<256, MODE, __nv_bfloat16, 2>(ma, mb, g, grid, st);
+    if (bn == 256 && c_dtype == DLB_F16) return launch_one<256, MODE, __half, 2>(ma, mb, g, grid, st);
+    return fail(DLB_ERR_INVALID, "256-row tiles need 256-wide tiles and a 16-bit output");
+  }
   if (bn == 256) {
     if (c_dtype == DLB_BF16) return launch_one<256, MODE, __nv_bfloat16>(ma, mb, g, grid, st);
     if (c_dtype == DLB_F16) return launch_one<256, MODE, __half>(ma, mb, g, grid, st);
@@ -630,7 +706,7 @@ using namespace dlb;
 
 extern "C" int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int64_t a_s_row_stride,
                             int64_t a_s_kb_stride, const float* b_s, void* c, int c_dtype, int64_t m, int64_t n,
-                            int64_t k, int32_t* status, void* stream) {
+                            int64_t k, int tile_rows, int32_t* status, void* stream) {
   DLB_REQUIRE(m >= 0 && n > 0 && k > 0, DLB_ERR_INVALID, "fp8_gemm: bad sizes m=%lld n=%lld k=%lld", (long long)m,
               (long long)n, (long long)k);
   DLB_REQUIRE(k % 128 == 0, DLB_ERR_INVALID, "fp8_gemm: k=%lld must be a multiple of 128", (long long)k);
@@ -645,11 +721,17 @@ extern "C" int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int6
   CUtensorMap ma, mb;
   if ((rc = make_map(&ma, a, (uint64_t)m, (uint64_t)k)) != DLB_OK) return rc;
   if ((rc = make_map(&mb, b, (uint64_t)n, (uint64_t)k)) != DLB_OK) return rc;
+  DLB_REQUIRE(tile_rows == 0 || tile_rows == 128 || tile_rows == 256, DLB_ERR_INVALID,
+              "fp8_gemm: tile_rows must be 0 (choose), 128 or 256");
   const int sms = sm_count();
-  const int m_tiles = (int)ceil_div(m, BM);
+  // Pairs of CTAs only on request: with one hand-shake per K block between the MMA warp of the leader and the
+  // promotion warps of both CTAs, the cluster-wide signalling doubles the K-block period (measured: 1.04 against
+  // 1.96 PFLOP/s on 8192 x 4096 x 7168), although the MMAs themselves get cheaper.
+  const int ctas = tile_rows == 256 ? 2 : 1;
+  const int m_tiles = (int)ceil_div(m, (int64_t)(ctas * BM));
   // 256-wide tiles feed the tensor cores best; fall back to 128 when that would leave SMs idle
   int bn = 256;
-  if (m_tiles * ceil_div(n, 256) < sms) bn = 128;
+  if (ctas == 1 && m_tiles * ceil_div(n, 256) < sms) bn = 128;
   GemmArgs g = {};
   g.a_s = a_s;
   g.a_s_rs = a_s_row_stride;
@@ -667,13 +749,14 @@ extern "C" int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int6
   g.status = status;
   g.timeout_cycles = DEFAULT_TIMEOUT_CYCLES;
   const long long total = (long long)m_tiles * g.num_n_tiles;
-  const int grid = (int)(total < sms ? total : sms);
-  return launch_typed<DLB_EPI_STORE>(bn, c_dtype, ma, mb, g, grid, (cudaStream_t)stream);
+  const int workers = sms / ctas;
+  const int grid = ctas * (int)(total < workers ? total : workers);
+  return launch_typed<DLB_EPI_STORE>(bn, ctas, c_dtype, ma, mb, g, grid, (cudaStream_t)stream);
 }
 
 extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a, const void* b, const float* b_s,
                                     int num_local_experts, int64_t n, int64_t k, const int32_t* tiles, int max_tiles,
-                                    int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
+                                    int tile_rows, int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
                                     int quant_mode, float quant_eps,
                                     const int64_t* sorted_idx, const float* weights, int32_t* status, void* stream) {
   DLB_REQUIRE(rows_a >= 0 && n > 0 && k > 0 && num_local_experts > 0 && max_tiles >= 0, DLB_ERR_INVALID,
@@ -714,6 +797,8 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t row
   g.weights = weights;
   g.status = status;
   g.timeout_cycles = DEFAULT_TIMEOUT_CYCLES;
+  DLB_REQUIRE(tile_rows == 128 || tile_rows == 256, DLB_ERR_INVALID, "grouped_gemm: tile_rows must be 128 or 256");
+  const int ctas = tile_rows / BM;
   int bn = 256;
   if (epilogue == DLB_EPI_SWIGLU_QUANT) {
     DLB_REQUIRE(n % 256 == 0, DLB_ERR_INVALID, "grouped_gemm: swiglu epilogue needs n %% 256 == 0 (n=%lld)",
@@ -727,13 +812,15 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t row
     if (epilogue == DLB_EPI_SCATTER_WEIGHT)
       DLB_REQUIRE(sorted_idx && weights, DLB_ERR_INVALID, "grouped_gemm: scatter epilogue needs sorted_idx and weights");
     DLB_REQUIRE(ldc % 8 == 0, DLB_ERR_INVALID, "grouped_gemm: ldc must be a multiple of 8");
-    if ((long long)max_tiles * ceil_div(n, 256) < sms) bn = 128;
+    if (ctas == 1 && (long long)max_tiles * ceil_div(n, 256) < sms) bn = 128;
     g.num_n_tiles = (int)ceil_div(n, bn);
   }
   const long long total = (long long)max_tiles * g.num_n_tiles;
-  const int grid = (int)(total < sms ? total : sms);
+  const int workers = sms / ctas;
+  const int grid = ctas * (int)(total < workers ? total : workers);
   cudaStream_t st = (cudaStream_t)stream;
-  if (epilogue == DLB_EPI_STORE) return launch_typed<DLB_EPI_STORE>(bn, c_dtype, ma, mb, g, grid, st);
-  if (epilogue == DLB_EPI_SCATTER_WEIGHT) return launch_typed<DLB_EPI_SCATTER_WEIGHT>(bn, c_dtype, ma, mb, g, grid, st);
-  return launch_typed<DLB_EPI_SWIGLU_QUANT>(bn, c_dtype, ma, mb, g, grid, st);
+  if (epilogue == DLB_EPI_STORE) return launch_typed<DLB_EPI_STORE>(bn, ctas, c_dtype, ma, mb, g, grid, st);
+  if (epilogue == DLB_EPI_SCATTER_WEIGHT)
+    return launch_typed<DLB_EPI_SCATTER_WEIGHT>(bn, ctas, c_dtype, ma, mb, g, grid, st);
+  return launch_typed<DLB_EPI_SWIGLU_QUANT>(bn, ctas, c_dtype, ma, mb, g, grid, st);
 }

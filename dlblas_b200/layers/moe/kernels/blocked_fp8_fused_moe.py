@@ -6,6 +6,7 @@ Pipeline of `moe_expert_forward` (all kernels from the CUDA extension, one launc
   grouped GEMM w13 with the silu*up + FP8 re-quantisation epilogue -> grouped GEMM w2 with the routed-weight
   epilogue scattered back to (token, slot) order -> sum over the top-k slots.
 """
+import os
 from typing import Optional
 
 import torch
@@ -47,8 +48,14 @@ def moe_expert_forward(hidden: Optional[torch.Tensor], x_q: Optional[torch.Tenso
     if weights.dtype != torch.float32:
         weights = weights.float()
     sorted_idx, exp_start, exp_end, pos = ops.sort_by_expert(ids, num_experts, want_pos=True)
-    max_tiles = ops.max_tiles_for(s_rows, e_local)
-    tiles = ops.build_tiles(exp_start, exp_end, expert_offset, e_local, max_tiles)
+    # DLBLAS_FP8_TILE_ROWS=256 runs the GEMMs on pairs of CTAs with 256-row tiles (tcgen05 cta_group::2).  Off by
+    # default: the per-K-block hand-shake across the two CTAs costs more than the cheaper MMAs win (0.94 against
+    # 1.85 PFLOP/s on 32 experts of 2048 rows); the variant is kept, bit-identical, for kernels with fewer hand-shakes.
+    tile_rows = int(os.environ.get("DLBLAS_FP8_TILE_ROWS", "0")) or 128
+    if out_dtype == torch.float32:
+        tile_rows = 128
+    max_tiles = ops.max_tiles_for(s_rows, e_local, tile_rows)
+    tiles = ops.build_tiles(exp_start, exp_end, expert_offset, e_local, max_tiles, tile_rows)
     if hidden is not None:
         a1, a1_s = ops.quant_fp8(hidden, group_size, quant_mode, 1e-10, False, pos, topk, s_rows)
     else:
@@ -57,14 +64,14 @@ def moe_expert_forward(hidden: Optional[torch.Tensor], x_q: Optional[torch.Tenso
     h_s = torch.empty(s_rows, inter // 128, dtype=torch.float32, device=dev)
     if fuse_swiglu and n % 256 == 0:
         ops.grouped_gemm(a1, a1_s, w1, w1_scale, tiles, max_tiles, _C.EPI_SWIGLU_QUANT, h_q, q_scale=h_s,
-                         round_dtype=out_dtype, quant_mode=quant_mode, quant_eps=1e-10)
+                         round_dtype=out_dtype, quant_mode=quant_mode, quant_eps=1e-10, tile_rows=tile_rows)
     else:
         c1 = torch.empty(s_rows, n, dtype=out_dtype, device=dev)
-        ops.grouped_gemm(a1, a1_s, w1, w1_scale, tiles, max_tiles, _C.EPI_STORE, c1)
+        ops.grouped_gemm(a1, a1_s, w1, w1_scale, tiles, max_tiles, _C.EPI_STORE, c1, tile_rows=tile_rows)
         ops.silu_mul_quant(c1, quant_mode, 1e-10, False, None, h_q, h_s)
     y = torch.empty(s_rows, h, dtype=out_dtype, device=dev)
     ops.grouped_gemm(h_q, h_s, w2, w2_scale, tiles, max_tiles, _C.EPI_SCATTER_WEIGHT, y, sorted_idx=sorted_idx,
-                     weights=weights)
+                     weights=weights, tile_rows=tile_rows)
     return ops.sum_topk(y, m, topk, ids, expert_offset, expert_offset + e_local, skip_unrouted_rows)
 
 

@@ -4,6 +4,8 @@ the CUDA extension.  The modules that mirror the reference's layout
 (`dlblas_b200.kernels.*`, `dlblas_b200.layers.moe.*`) are built on these."""
 from typing import Optional, Tuple
 
+import os
+
 import torch
 
 from . import _C
@@ -39,15 +41,15 @@ def sort_by_expert(topk_ids: torch.Tensor, num_experts: int, want_pos=False, wan
     return tuple(out)
 
 
-def max_tiles_for(num_rows: int, num_local_experts: int) -> int:
-    return num_rows // 128 + num_local_experts
+def max_tiles_for(num_rows: int, num_local_experts: int, tile_rows: int = 128) -> int:
+    return num_rows // tile_rows + num_local_experts
 
 
 def build_tiles(exp_start: torch.Tensor, exp_end: torch.Tensor, expert_offset: int, num_local_experts: int,
-                max_tiles: int) -> torch.Tensor:
+                max_tiles: int, tile_rows: int = 128) -> torch.Tensor:
     tiles = torch.empty((max_tiles + 1) * 4, dtype=torch.int32, device=exp_start.device)
-    check(lib().dlb_moe_build_tiles(ptr(exp_start), ptr(exp_end), expert_offset, num_local_experts, ptr(tiles),
-                                    max_tiles, stream(exp_start.device)))
+    check(lib().dlb_moe_build_tiles_rows(ptr(exp_start), ptr(exp_end), expert_offset, num_local_experts, int(tile_rows),
+                                         ptr(tiles), max_tiles, stream(exp_start.device)))
     return tiles
 
 
@@ -136,8 +138,13 @@ def silu_mul_quant(gate_up: torch.Tensor, mode: int = _C.QUANT_RECIP_MUL, eps: f
 
 # --------------------------------------------------------------------------- GEMMs
 def fp8_gemm(a: torch.Tensor, b: torch.Tensor, a_s: torch.Tensor, b_s: torch.Tensor,
-             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+             out_dtype: torch.dtype = torch.bfloat16, tile_rows: Optional[int] = None) -> torch.Tensor:
+    """tile_rows: 128 / 256 (pairs of CTAs) / None = DLBLAS_FP8_TILE_ROWS or the library's choice."""
     require_cuda(a, b, a_s, b_s)
+    if tile_rows is None:
+        tile_rows = int(os.environ.get("DLBLAS_FP8_TILE_ROWS", "0"))
+    if out_dtype == torch.float32:
+        tile_rows = 128
     assert a.is_contiguous() and b.is_contiguous(), "Input tensors must be contiguous"
     assert a_s.is_contiguous() and b_s.is_contiguous(), "Scaling factor tensors must be contiguous"
     k = a.size(-1)
@@ -148,7 +155,7 @@ def fp8_gemm(a: torch.Tensor, b: torch.Tensor, a_s: torch.Tensor, b_s: torch.Ten
     a_s2 = a_s.view(m, -1) if m > 0 else a_s
     assert a_s.numel() == m * kb and b_s.numel() == ((n + 127) // 128) * kb, "scale shapes do not match a / b"
     check(lib().dlb_fp8_gemm(ptr(a), ptr(b), ptr(a_s2), kb, 1, ptr(b_s), ptr(c), dtype_code(out_dtype), m, n, k,
-                             ptr(_C.status_word(a.device)), stream(a.device)))
+                             int(tile_rows), ptr(_C.status_word(a.device)), stream(a.device)))
     return c
 
 
@@ -156,8 +163,9 @@ def grouped_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch
                  max_tiles: int, epilogue: int, c: torch.Tensor, q_scale: Optional[torch.Tensor] = None,
                  sorted_idx: Optional[torch.Tensor] = None, weights: Optional[torch.Tensor] = None,
                  round_dtype: Optional[torch.dtype] = None, quant_mode: int = _C.QUANT_RECIP_MUL,
-                 quant_eps: float = 1e-10):
-    """a [rows, k] e4m3 in expert-contiguous order, b [E, n, k]; see dlb_moe_grouped_gemm."""
+                 quant_eps: float = 1e-10, tile_rows: int = 128):
+    """a [rows, k] e4m3 in expert-contiguous order, b [E, n, k]; `tiles` built with the same `tile_rows`;
+    see dlb_moe_grouped_gemm."""
     require_cuda(a, b)
     assert a.is_contiguous() and a_s.is_contiguous() and b.is_contiguous() and b_s.is_contiguous()
     assert c.stride(-1) == 1
@@ -167,7 +175,8 @@ def grouped_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch
         cdt = dtype_code(round_dtype or torch.bfloat16)
     else:
         cdt = dtype_code(c.dtype)
-    check(lib().dlb_moe_grouped_gemm(ptr(a), ptr(a_s), rows, ptr(b), ptr(b_s), e, n, k, ptr(tiles), max_tiles, epilogue,
+    check(lib().dlb_moe_grouped_gemm(ptr(a), ptr(a_s), rows, ptr(b), ptr(b_s), e, n, k, ptr(tiles), max_tiles,
+                                     int(tile_rows), epilogue,
                                      ptr(c), cdt, c.stride(0), ptr(q_scale), quant_mode, quant_eps, ptr(sorted_idx),
                                      ptr(weights),
                                      ptr(_C.status_word(a.device)), stream(a.device)))

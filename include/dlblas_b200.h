@@ -147,22 +147,24 @@ DLB_API int dlb_silu_mul_quant(const void* gate_up, int dtype, int64_t rows, int
  * fp8_gemm (dlblas/kernels/fp8_gemm.py:17-89): C[m,n] = sum_kb (A_kb . B_kb^T) a_s[m,kb] b_s[n/128,kb].
  * a: [m,k] e4m3 row-major, b: [n,k] e4m3 row-major, a_s fp32 at a_s[row*a_s_row_stride + kb*a_s_kb_stride],
  * b_s fp32 [ceil(n/128), k/128] row-major, c: [m,n] of c_dtype (DLB_BF16/F16/F32).  k % 128 == 0,
- * n % 8 == 0.  status (may be NULL): device int set to DLB_STATUS_TIMEOUT if a bounded wait gave up. */
+ * n % 8 == 0.  tile_rows: 0 or 128 = one CTA per 128-row tile, 256 = pairs of CTAs on 256-row tiles (tcgen05
+ * cta_group::2; 16-bit outputs only; same results, currently slower: see gemm_fp8.cu).  status (may be NULL): device int set
+ * to DLB_STATUS_TIMEOUT if a bounded wait gave up. */
 DLB_API int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int64_t a_s_row_stride, int64_t a_s_kb_stride,
-                 const float* b_s, void* c, int c_dtype, int64_t m, int64_t n, int64_t k, int32_t* status,
-                 void* stream);
+                 const float* b_s, void* c, int c_dtype, int64_t m, int64_t n, int64_t k, int tile_rows,
+                 int32_t* status, void* stream);
 
 /* Grouped GEMM over ragged expert segments; replaces fused_moe_blocked_f8_kernel + launcher
  * (dlblas/layers/moe/kernels/blocked_fp8_fused_moe.py:30-242) and the DeepGEMM calls
  * m_grouped_fp8_gemm_nt_contiguous / _masked (dlblas/kernels/fused_moe_v3.py:235-245,
  * dlblas/layers/moe/ep_moe.py:180-197).  a: [rows_a, k] e4m3 in expert-contiguous order,
  * a_s: [rows_a, k/128]; b: [experts, n, k] e4m3; b_s: [experts, n/128, k/128]; tiles from
- * dlb_moe_build_tiles*.  Epilogues: see DLB_EPI_*.  For DLB_EPI_SWIGLU_QUANT n is the width of
+ * dlb_moe_build_tiles* with tiles of `tile_rows` rows (128, or 256 = pairs of CTAs: same results, currently slower).  Epilogues: see DLB_EPI_*.  For DLB_EPI_SWIGLU_QUANT n is the width of
  * b (2 * intermediate, gate rows first), c receives e4m3 [rows_a, n/2] and q_scale fp32 [rows_a, n/256];
  * quant_mode / quant_eps choose the scale arithmetic of that re-quantisation (DLB_QUANT_*). */
 DLB_API int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a, const void* b, const float* b_s,
                          int num_local_experts, int64_t n, int64_t k, const int32_t* tiles, int max_tiles,
-                         int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
+                         int tile_rows, int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
                          int quant_mode, float quant_eps,
                          const int64_t* sorted_idx, const float* weights, int32_t* status, void* stream);
 

@@ -33,7 +33,7 @@ def test_argument_validation_without_gpu():
     """Size / dtype checks run before any CUDA call and report through the error string."""
     from dlblas_b200 import _C
     lib = _C.lib()
-    assert lib.dlb_fp8_gemm(None, None, None, 1, 1, None, None, _C.DLB_BF16, 4, 128, 100, None, None) == -1
+    assert lib.dlb_fp8_gemm(None, None, None, 1, 1, None, None, _C.DLB_BF16, 4, 128, 100, 0, None, None) == -1
     assert b"multiple of 128" in lib.dlb_last_error_string()
     assert lib.dlb_quant_fp8(None, _C.DLB_BF16, 4, 100, 100, 128, 0, 0.0, None, None, 1, 1, None, 1, None) == -1
     assert lib.dlb_sort_by_expert(None, _C.DLB_F32, 8, 4, None, None, None, None, None, None, None, 0, None) == -1
