@@ -474,6 +474,18 @@ def run_profile(args):
         torch.cuda.synchronize()
         _C.check_status(dev)
         return
+    if args.profile == "gemm16":
+        # 16-bit grouped GEMM (whole K accumulated in TMEM, pairs of CTAs): `experts` groups of `tokens` rows in all
+        from dlblas_b200.kernels.grouped_gemm.BF16 import m_grouped_gemm
+        gd = torch.Generator(device=dev).manual_seed(7)
+        a = torch.randn(t, H, generator=gd, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(e, 2 * INTER, H, generator=gd, device=dev, dtype=torch.bfloat16) * 0.05
+        sizes = torch.full((e,), t // e, device=dev, dtype=torch.int64)
+        for _ in range(args.steps):
+            m_grouped_gemm(a, b, sizes, trans_b=True)
+        torch.cuda.synchronize()
+        _C.check_status(dev)
+        return
     w13, w13s, w2, w2s = make_weights(e, 1, dev)
     x = torch.randn(t, H, generator=g).to(torch.bfloat16).to(dev)
     ids = torch.stack([torch.randperm(e, generator=g)[:TOPK] for _ in range(t)]).to(dev)
@@ -586,7 +598,7 @@ def run_decode(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile", default="", choices=["", "gemm1", "gemm2", "dense"],
+    ap.add_argument("--profile", default="", choices=["", "gemm1", "gemm2", "dense", "gemm16"],
                     help="run only one kernel on a small case (for ncu) and exit")
     ap.add_argument("--experts", type=int, default=32, help="experts of the --profile case")
     ap.add_argument("--gpus", type=int, default=1)
