@@ -217,31 +217,39 @@ __global__ void __launch_bounds__(THREADS) silu_mul_quant_kernel(const T* __rest
   }
 }
 
+// One warp per token: the slots' ids are read once per warp (lane j holds slot j), rows nobody routed to cost
+// one load, and the lanes sweep the row's columns together (512 contiguous bytes per load instruction).
 template <typename T, typename IdT>
 __global__ void __launch_bounds__(THREADS) sum_topk_kernel(const T* __restrict__ y, long long tokens, int top_k,
                                                            long long h, const IdT* __restrict__ ids, long long id_lo,
                                                            long long id_hi, int skip_unrouted, T* __restrict__ out) {
-  const long long vec_per_row = h / 8;
-  const long long total = tokens * vec_per_row;
-  for (long long u = (long long)blockIdx.x * THREADS + threadIdx.x; u < total; u += (long long)gridDim.x * THREADS) {
-    const long long t = u / vec_per_row;
-    const long long c = (u - t * vec_per_row) * 8;
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    bool any = false;
-    for (int j = 0; j < top_k; ++j) {
-      if (ids != nullptr) {
-        const long long id = (long long)ids[t * top_k + j];
-        if (id < id_lo || id >= id_hi) continue;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (THREADS / 32);
+  for (long long t = (long long)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5); t < tokens; t += warps) {
+    unsigned live = 0xffffffffu;                       // bit j: slot j contributes
+    if (ids != nullptr) {
+      bool in_range = false;
+      if (lane < top_k) {                              // top_k <= 32 (checked by the caller)
+        const long long id = (long long)ids[t * top_k + lane];
+        in_range = id >= id_lo && id < id_hi;
       }
-      any = true;
-      float v[8];
-      Vec8<T>::load(y + (t * top_k + j) * h + c, v);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += v[i];
+      live = __ballot_sync(0xffffffffu, in_range);
     }
-    if (any || !skip_unrouted) Vec8<T>::store(out + t * h + c, acc);   // rows nobody routed to: zeros, or left alone
+    if (top_k < 32) live &= (1u << top_k) - 1u;
+    if (live == 0u && skip_unrouted) continue;         // rows nobody routed to are left alone
+    for (long long c = (long long)lane * 8; c < h; c += 256) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int j = 0; j < top_k; ++j) {
+        if (!((live >> j) & 1u)) continue;
+        float v[8];
+        Vec8<T>::load(y + (t * top_k + j) * h + c, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += v[i];
+      }
+      Vec8<T>::store(out + t * h + c, acc);
+    }
   }
 }
 
@@ -532,7 +540,7 @@ namespace {
 template <typename T>
 int launch_sum_topk(const void* y, int64_t tokens, int top_k, int64_t h, const void* ids, int ids_dtype, int64_t lo,
                     int64_t hi, int skip, void* out, cudaStream_t st) {
-  const int grid = grid_for(tokens * (h / 8));
+  const int grid = grid_for(tokens * 32);          // one warp per token
   if (ids != nullptr && ids_dtype == DLB_I32)
     sum_topk_kernel<T, int><<<grid, THREADS, 0, st>>>(reinterpret_cast<const T*>(y), tokens, top_k, h,
                                                      reinterpret_cast<const int*>(ids), lo, hi, skip,
@@ -550,8 +558,8 @@ int launch_sum_topk(const void* y, int64_t tokens, int top_k, int64_t h, const v
 extern "C" int dlb_moe_sum_topk(const void* y, int dtype, int64_t tokens, int top_k, int64_t h, const void* ids,
                                 int ids_dtype, int64_t id_lo, int64_t id_hi, int skip_unrouted_rows, void* out,
                                 void* stream) {
-  DLB_REQUIRE(tokens >= 0 && top_k > 0 && h > 0 && h % 8 == 0, DLB_ERR_INVALID,
-              "sum_topk: h=%lld must be a positive multiple of 8", (long long)h);
+  DLB_REQUIRE(tokens >= 0 && top_k > 0 && top_k <= 32 && h > 0 && h % 8 == 0, DLB_ERR_INVALID,
+              "sum_topk: h=%lld must be a positive multiple of 8 and top_k=%d at most 32", (long long)h, top_k);
   DLB_REQUIRE(ids == nullptr || ids_dtype == DLB_I32 || ids_dtype == DLB_I64, DLB_ERR_INVALID,
               "sum_topk: ids must be int32/int64");
   if (tokens == 0) return DLB_OK;
