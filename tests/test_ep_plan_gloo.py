@@ -134,3 +134,8 @@ def test_single_rank_plan_without_process_group():
     assert plan.recv_tokens_per_expert == [128, 128, 128, 128]
     lp = td.make_low_latency_plan(torch.tensor([1, 2, 0, 1]), 1, 0, 4, None, 8)
     assert lp.masked_m.tolist() == [1, 2, 0, 1] and lp.recv_dst.tolist() == [0, 8, 9, 24]
+    # the device-side plan of a world of one: same destinations, buffers sized for every (token, slot) pair,
+    # pairs without an expert (they sort to the end of the send order) dropped
+    sp = td.make_single_rank_plan(torch.tensor([1, 2, 0, 1]), 6, 8)
+    assert sp.masked_m.tolist() == [1, 2, 0, 1] and sp.num_send == sp.num_recv == 6
+    assert sp.recv_dst.tolist() == [0, 8, 9, 24, -1, -1]
