@@ -53,6 +53,7 @@ SIGNATURES = {
     "dlb_p2p_quant_push": (c_int, [c_vp, c_int, c_i64, c_i64, c_i64, c_int, c_f, c_vp, c_int, c_int, c_i64, c_vp, c_vp,
                                    c_vp, c_vp, c_int, c_vp, c_vp, c_vp]),
     "dlb_p2p_unpack_meta": (c_int, [c_vp, c_int, c_int, c_vp, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
+    "dlb_p2p_sum_push": (c_int, [c_vp, c_int, c_vp, c_int, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
     "dlb_p2p_push_rows": (c_int, [c_vp, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
     "dlb_grouped_gemm_16bit": (c_int, [c_vp, c_vp, c_int, c_i64, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_vp, c_i64,
                                        c_vp, c_vp]),

@@ -136,6 +136,45 @@ __global__ void __launch_bounds__(THREADS) push_rows_kernel(const uint4* __restr
   }
 }
 
+// Combine step of the expert side, fused with the push: for every received row (row j of region s, j < counts[s])
+// the results of its slots on local experts are summed in fp32 in slot order, rounded to bf16 / fp16 and stored
+// straight into the source rank's combine buffer (region "my rank", row j).  One warp per row; ids are the
+// local expert ids of the row's slots (negative = another rank's expert).
+template <typename T>
+__global__ void __launch_bounds__(THREADS) sum_push_kernel(const T* __restrict__ y, const long long* __restrict__ ids,
+                                                           int top_k, long long h, const int* __restrict__ counts,
+                                                           int world, int my_rank, long long region_rows,
+                                                           PeerPtrs peer_dst) {
+  const int lane = threadIdx.x & 31;
+  const long long rows = (long long)world * region_rows;
+  const long long warps = (long long)gridDim.x * (THREADS / 32);
+  for (long long r = (long long)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const int s = (int)(r / region_rows);
+    const long long j = r - (long long)s * region_rows;
+    if (j >= counts[s]) continue;
+    const bool mine = lane < top_k && ids[r * top_k + lane] >= 0;
+    const unsigned live = __ballot_sync(0xffffffffu, mine);
+    T* dst = reinterpret_cast<T*>(peer_dst.p[s]) + ((long long)my_rank * region_rows + j) * h;
+    for (long long c = (long long)lane * 8; c < h; c += 256) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int q = 0; q < top_k; ++q) {
+        if (!((live >> q) & 1u)) continue;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(y + (r * top_k + q) * h + c));
+        const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(v[i]);
+      }
+      uint4 out;
+      T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = from_f32<T>(acc[i]);
+      *reinterpret_cast<uint4*>(dst + c) = out;
+    }
+  }
+}
+
 int grid_for(long long total_threads) {
   long long blocks = ceil_div(total_threads, THREADS);
   const long long cap = (long long)sm_count() * 16;
@@ -226,5 +265,32 @@ extern "C" int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32
       reinterpret_cast<const uint4*>(src), vpr, counts, world, my_rank, region_rows, pd);
   count_launch();
   DLB_CHECK_LAUNCH("push_rows_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_p2p_sum_push(const void* y, int dtype, const int64_t* ids, int top_k, int64_t h, const int32_t* counts,
+                                int world, int my_rank, int64_t region_rows, const void* const* peer_dst, void* stream) {
+  DLB_REQUIRE(world > 0 && world <= MAX_WORLD && my_rank >= 0 && my_rank < world && region_rows > 0, DLB_ERR_INVALID,
+              "p2p_sum_push: bad world / rank / region");
+  DLB_REQUIRE(top_k > 0 && top_k <= 32 && h > 0 && h % 8 == 0, DLB_ERR_INVALID,
+              "p2p_sum_push: top_k=%d must be in [1, 32] and h=%lld a multiple of 8", top_k, (long long)h);
+  DLB_REQUIRE(dtype == DLB_BF16 || dtype == DLB_F16, DLB_ERR_INVALID, "p2p_sum_push: dtype must be bf16 or fp16");
+  DLB_REQUIRE(y && ids && counts, DLB_ERR_INVALID, "p2p_sum_push: null pointer");
+  DLB_REQUIRE((uintptr_t)y % 16 == 0, DLB_ERR_INVALID, "p2p_sum_push: y must be 16-byte aligned");
+  PeerPtrs pd;
+  int rc = fill_peers(pd, peer_dst, world, "p2p_sum_push");
+  if (rc != DLB_OK) return rc;
+  const int grid = grid_for((long long)world * region_rows * 32);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == DLB_BF16)
+    sum_push_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(y),
+                                                            reinterpret_cast<const long long*>(ids), top_k, h, counts,
+                                                            world, my_rank, region_rows, pd);
+  else
+    sum_push_kernel<__half><<<grid, THREADS, 0, st>>>(reinterpret_cast<const __half*>(y),
+                                                     reinterpret_cast<const long long*>(ids), top_k, h, counts, world,
+                                                     my_rank, region_rows, pd);
+  count_launch();
+  DLB_CHECK_LAUNCH("sum_push_kernel");
   return DLB_OK;
 }

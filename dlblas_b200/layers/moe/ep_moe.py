@@ -68,9 +68,12 @@ class FusedMoENormal:
 
     def _p2p_experts(self, d, hs, topk_ids, topk_weights, up_weights, up_scale, down_weights, down_scale):
         (rq, rs), rids, rw = d.dispatch_from_hidden(hs, topk_ids, topk_weights, self.block_size)
+        fused = os.environ.get("DLBLAS_EP_FUSED_COMBINE", "1") == "1"
         out_rows = moe_expert_forward(None, rq, rs, up_weights, up_scale, down_weights, down_scale, rw, rids,
                                       topk_ids.shape[1], hs.dtype, 0, self.num_local_experts,
-                                      _C.QUANT_DIV_EPS, skip_unrouted_rows=True)
+                                      _C.QUANT_DIV_EPS, skip_unrouted_rows=True, return_slot_rows=fused)
+        if fused:
+            return d.combine_slots(out_rows, rids)      # sum over a row's local slots while pushing it back
         return d.combine(out_rows)
 
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,

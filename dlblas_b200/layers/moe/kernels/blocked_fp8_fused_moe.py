@@ -28,7 +28,7 @@ def moe_expert_forward(hidden: Optional[torch.Tensor], x_q: Optional[torch.Tenso
                        expert_offset: int = 0, num_experts: Optional[int] = None,
                        quant_mode: int = _C.QUANT_RECIP_MUL, weighted_combine: bool = False,
                        fuse_swiglu: bool = True, group_size: int = 128,
-                       skip_unrouted_rows: bool = False) -> torch.Tensor:
+                       skip_unrouted_rows: bool = False, return_slot_rows: bool = False) -> torch.Tensor:
     """Expert computation for tokens that are either unquantised (`hidden` [M, H]) or already
     quantised (`x_q` e4m3 [M, H], `x_s` fp32 [M, H/128]).  topk_ids are global ids in
     [expert_offset, expert_offset + E_local) for the experts held in w1/w2; any other id (e.g. -1)
@@ -72,6 +72,10 @@ def moe_expert_forward(hidden: Optional[torch.Tensor], x_q: Optional[torch.Tenso
     y = torch.empty(s_rows, h, dtype=out_dtype, device=dev)
     ops.grouped_gemm(h_q, h_s, w2, w2_scale, tiles, max_tiles, _C.EPI_SCATTER_WEIGHT, y, sorted_idx=sorted_idx,
                      weights=weights, tile_rows=tile_rows)
+    if return_slot_rows:
+        # [M * topk, H] rows of the individual (token, slot) results, already weighted; the caller sums them
+        # (the expert-parallel combine does it while pushing the rows to their source rank)
+        return y
     return ops.sum_topk(y, m, topk, ids, expert_offset, expert_offset + e_local, skip_unrouted_rows)
 
 

@@ -494,11 +494,29 @@ class TokenDispatcherP2P:
         _C.check(_C.lib().dlb_p2p_push_rows(_C.ptr(out_rows), self.hidden_size * out_rows.element_size(),
                                            _C.ptr(self.recv_counts), w, self.rank, self.region_rows,
                                            self._peers["comb"], _C.stream(dev)))
+        return self._finish_combine(within, t, out_rows.dtype, dev)
+
+    def combine_slots(self, slot_rows: torch.Tensor, recv_ids: torch.Tensor) -> torch.Tensor:
+        """slot_rows: [world * max_tokens_per_rank * k, H] weighted results of the individual (row, slot) pairs,
+        recv_ids int64 [rows, k] the local expert ids from `dispatch_from_hidden`.  Sums a row's slots and
+        stores the sum into the source rank's buffer in one kernel (no intermediate [rows, H] tensor)."""
+        within, t = self.handle
+        w, dev = self.world_size, slot_rows.device
+        k = recv_ids.shape[1]
+        assert slot_rows.is_contiguous() and slot_rows.shape == (self.rows * k, self.hidden_size)
+        assert slot_rows.dtype == self.comb.dtype and recv_ids.dtype == torch.int64 and recv_ids.is_contiguous()
+        _C.check(_C.lib().dlb_p2p_sum_push(_C.ptr(slot_rows), _C.dtype_code(slot_rows.dtype), _C.ptr(recv_ids), k,
+                                          self.hidden_size, _C.ptr(self.recv_counts), w, self.rank, self.region_rows,
+                                          self._peers["comb"], _C.stream(dev)))
+        return self._finish_combine(within, t, slot_rows.dtype, dev)
+
+    def _finish_combine(self, within, t, dtype, dev):
+        w = self.world_size
         self._hdl.barrier(channel=1)
         base = (torch.arange(w, device=dev, dtype=torch.int32) * self.region_rows)[None, :]
         idx = torch.where(within >= 0, within + base, torch.full_like(within, -1)).contiguous()
         ones = torch.ones(t, w, dtype=torch.float32, device=dev)
-        out = torch.empty(t, self.hidden_size, dtype=out_rows.dtype, device=dev)
+        out = torch.empty(t, self.hidden_size, dtype=dtype, device=dev)
         # out[t] = sum over the ranks the token visited, in rank order (fp32 accumulation)
         ops.ep_gather(self.comb, idx, ones, idx, out)
         self.handle = None

@@ -220,6 +220,11 @@ DLB_API int dlb_p2p_unpack_meta(const int32_t* meta, int meta_ints, int top_k, c
                         void* stream);
 DLB_API int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32_t* counts, int world, int my_rank,
                       int64_t region_rows, const void* const* peer_dst, void* stream);
+/* Expert-side combine fused with the push: out row = sum (fp32, slot order) of y[row * top_k + q] over the slots q
+ * whose local expert id ids[row, q] is >= 0, rounded to dtype and stored into the source rank's buffer like
+ * dlb_p2p_push_rows does.  y [rows * top_k, h] bf16 / fp16, ids int64 [rows, top_k]. */
+DLB_API int dlb_p2p_sum_push(const void* y, int dtype, const int64_t* ids, int top_k, int64_t h, const int32_t* counts,
+                     int world, int my_rank, int64_t region_rows, const void* const* peer_dst, void* stream);
 
 /* ---- 16-bit grouped GEMM -----------------------------------------------------------------
  * m_grouped_gemm with trans_b = True (dlblas/kernels/grouped_gemm/BF16/m_grouped_gemm.py:235-352):

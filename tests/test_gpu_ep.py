@@ -50,6 +50,8 @@ def _worker(rank, world, port, ret):
             # two token chunks on two streams (ranks hold 96 and 128 tokens: chunks of 48 / 64)
             os.environ["DLBLAS_EP_MIN_CHUNK_ROWS"] = "32" if backend == "p2p-chunked" else "1024"
             os.environ["DLBLAS_EP_CHUNKS"] = "2" if backend == "p2p-chunked" else "1"
+            # the chunked run also takes the unfused combine (sum kernel, then push) so that both stay covered
+            os.environ["DLBLAS_EP_FUSED_COMBINE"] = "0" if backend == "p2p-chunked" else "1"
             backend = backend.split("-")[0]
             os.environ["DLBLAS_EP_BACKEND"] = backend
             layer = build_deepep_moe(low_latency, world, dist.group.WORLD, e, h, 128, k, torch.bfloat16)
