@@ -24,6 +24,131 @@ logger = get_logger(__name__)
 enable_moe_load_stats = os.environ.get("DLBLAS_MOE_LOAD_STATS", "false").lower() == "true"
 
 
+class DlblasTritonFusedMoEBlockedF8Impl:
+    """Block-scaled FP8 fused MoE layer (ep_moe.py:413-484).  The name is the reference's; the kernels
+    underneath are the sm_100a CUDA extension."""
+
+    def __init__(self, top_k: int, num_experts: int, renormalize: bool = False, block_size: int = 128,
+                 out_dtype: torch.dtype = torch.float16, ep_size: int = 1):
+        self.num_experts = num_experts
+        self.top_k = top_k
+        self.renormalize = renormalize
+        self.block_size = block_size
+        self.out_dtype = out_dtype
+        self.ep_size = ep_size
+
+    def support_ep(self):
+        return True
+
+    def ep_expert_list(self, world_size: int, rank: int):
+        per_rank = (self.num_experts + world_size - 1) // world_size
+        first = rank * per_rank
+        return list(range(first, min(first + per_rank, self.num_experts)))
+
+    def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,
+                gate_up_weights: torch.Tensor, gate_up_scale: torch.Tensor, down_weights: torch.Tensor,
+                down_scale: torch.Tensor, expert_list: List[int] = None):
+        """hidden_states [..., H] bf16/fp16; topk_ids local to this rank's experts (-1 elsewhere) when
+        `expert_list` is a strict subset, and then shifted by expert_list[0] in place as the reference does."""
+        input_size = hidden_states.shape
+        hidden_states = hidden_states.flatten(0, -2)
+        expert_offset = 0
+        num_experts = None
+        if expert_list is not None and len(expert_list) != self.num_experts:
+            expert_offset = expert_list[0]
+            num_experts = self.num_experts
+        e_local = gate_up_weights.shape[0]
+        if num_experts is None:
+            num_experts = e_local * self.ep_size if self.ep_size > 1 else e_local
+        topk_weights = _renormalize(topk_weights, self.renormalize)
+        if expert_offset != 0:
+            topk_ids[topk_ids != -1] += expert_offset
+        output = moe_expert_forward(hidden_states, None, None, gate_up_weights, gate_up_scale, down_weights,
+                                    down_scale, topk_weights, topk_ids, self.top_k, hidden_states.dtype,
+                                    expert_offset, num_experts, _C.QUANT_RECIP_MUL, group_size=self.block_size)
+        return output.unflatten(0, input_size[:-1])
+
+
+class FusedMoELowLatency:
+    """Expert-parallel decode layer on the masked layout [E_local, max_tokens * world, H]
+    (ep_moe.py:155-347): dispatch casts to FP8, the experts run two masked grouped GEMMs with the fused
+    silu*up + quantisation between them, combine applies the routing weights."""
+    recorder = ExpertsDistributionRecorder(output_dir="/tmp/dlblas/decode_moe_stats")
+
+    def __init__(self, ep_size: int, ep_group: dist.ProcessGroup, num_experts: int, hidden_dim: int,
+                 layer_index: int, block_size: int = 128, out_dtype: torch.dtype = torch.bfloat16):
+        self.num_experts = num_experts
+        self.layer_index = layer_index
+        self.block_size = block_size
+        self.out_dtype = out_dtype
+        self.token_dispatcher = TokenDispatcherLowLatency(group=ep_group, num_experts=num_experts,
+                                                          num_local_experts=num_experts // ep_size,
+                                                          hidden_size=hidden_dim, params_dtype=out_dtype)
+
+    def experts(self, hidden_states_fp8, gate_up_weight: torch.Tensor, gate_up_scale: torch.Tensor,
+                gate_down_weight: torch.Tensor, gate_down_scale: torch.Tensor, masked_m: torch.Tensor,
+                expected_m: int):
+        """Masked-layout expert MLP: x [E_local, rows, H] e4m3 + scales, only the first masked_m[e] rows of every
+        expert are valid.  `expected_m` (a scheduling hint of the reference's GEMM library) is not needed: the
+        tile list is built on the device from masked_m."""
+        x_q, x_s = hidden_states_fp8
+        e_local, rows, hidden = x_q.shape
+        width = gate_up_weight.size(1)                       # 2 * intermediate
+        inter = width // 2
+        dev = x_q.device
+        valid_rows = masked_m if masked_m.dtype == torch.int32 else masked_m.to(torch.int32)
+        tiles, max_tiles = ops.build_tiles_masked(valid_rows, rows)
+        flat = e_local * rows
+
+        def gemm(a_q, a_s, w, w_s, out):
+            ops.grouped_gemm(a_q, a_s, w, w_s, tiles, max_tiles, _C.EPI_STORE, out)
+
+        gate_up = torch.empty((e_local, rows, width), device=dev, dtype=self.out_dtype)
+        gemm(DisposibleTensor.maybe_unwrap(x_q).view(flat, hidden), DisposibleTensor.maybe_unwrap(x_s).view(flat, -1),
+             gate_up_weight, gate_up_scale, gate_up.view(flat, width))
+        # the dispatch buffers are the largest tensors of the decode step: give them back as early as the
+        # reference does (kernels already enqueued keep the memory alive through the caching allocator)
+        for t in hidden_states_fp8:
+            DisposibleTensor.maybe_dispose(t)
+        act_q = torch.empty((e_local, rows, inter), device=dev, dtype=gate_down_weight.dtype)
+        act_s = torch.empty((e_local, rows, inter // self.block_size), device=dev, dtype=torch.float32)
+        silu_and_mul_masked_post_quant_fwd(gate_up, act_q, act_s, self.block_size, valid_rows)
+        del gate_up
+        out = torch.empty((e_local, rows, gate_down_weight.size(1)), device=dev, dtype=self.out_dtype)
+        gemm(act_q.view(flat, inter), act_s.view(flat, -1), gate_down_weight, gate_down_scale, out.view(flat, -1))
+        return out
+
+    def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,
+                up_weights: torch.Tensor, up_scale: torch.Tensor, down_weights: torch.Tensor,
+                down_scale: torch.Tensor, expert_list: List[int] = None):
+        if enable_moe_load_stats:
+            FusedMoELowLatency.recorder.record(topk_ids, self.layer_index, self.num_experts)
+        recv_hidden_states, topk_idx, topk_weights, masked_m, expected_m = self.token_dispatcher.dispatch(
+            hidden_states, topk_ids, topk_weights, self.num_experts)
+        out_states = self.experts(recv_hidden_states, up_weights, up_scale, down_weights, down_scale, masked_m,
+                                  expected_m)
+        return self.token_dispatcher.combine(out_states, topk_idx, topk_weights)
+
+    def wait(self, event):
+        event.current_stream_wait()
+
+    def dispatch_async(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, num_experts: Optional[int] = None,
+                       use_fp8: bool = True, async_finish: bool = True):
+        return self.token_dispatcher.dispatch_async(hidden_states, topk_idx, num_experts, use_fp8, async_finish)
+
+    def combine_async(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+                      handle: tuple, async_finish: bool):
+        return self.token_dispatcher.combine_async(hidden_states, topk_idx, topk_weights, handle, async_finish)
+
+    def fusedmoe_forward(self, state, up_weight, up_scale, down_weight, down_scale):
+        hidden_shape = state["raw_hidden_shape"]
+        topk_idx = state["topk_idx"]
+        d = self.token_dispatcher
+        expected_m = (hidden_shape[0] * d.world_size * topk_idx.shape[1] + d.num_experts) // d.num_experts
+        return self.experts(state["recv_hidden_states"], up_weight, up_scale, down_weight, down_scale,
+                            state["recv_expert_count"], expected_m)
+
+
 class FusedMoENormal:
     """Expert-parallel prefill layer: quantise, dispatch to the ranks that own the routed experts,
     run the experts on the received tokens, combine back (ep_moe.py:34-152)."""
@@ -146,81 +271,6 @@ class FusedMoENormal:
         return per_token_group_quant_fp8(x, self.block_size)
 
 
-class FusedMoELowLatency:
-    """Expert-parallel decode layer on the masked layout [E_local, max_tokens * world, H]
-    (ep_moe.py:155-347): dispatch casts to FP8, the experts run two masked grouped GEMMs with the fused
-    silu*up + quantisation between them, combine applies the routing weights."""
-    recorder = ExpertsDistributionRecorder(output_dir="/tmp/dlblas/decode_moe_stats")
-
-    def __init__(self, ep_size: int, ep_group: dist.ProcessGroup, num_experts: int, hidden_dim: int,
-                 layer_index: int, block_size: int = 128, out_dtype: torch.dtype = torch.bfloat16):
-        self.num_experts = num_experts
-        self.layer_index = layer_index
-        self.block_size = block_size
-        self.out_dtype = out_dtype
-        self.token_dispatcher = TokenDispatcherLowLatency(group=ep_group, num_experts=num_experts,
-                                                          num_local_experts=num_experts // ep_size,
-                                                          hidden_size=hidden_dim, params_dtype=out_dtype)
-
-    def experts(self, hidden_states_fp8, gate_up_weight: torch.Tensor, gate_up_scale: torch.Tensor,
-                gate_down_weight: torch.Tensor, gate_down_scale: torch.Tensor, masked_m: torch.Tensor,
-                expected_m: int):
-        num_groups, m, k = hidden_states_fp8[0].shape
-        dev = hidden_states_fp8[0].device
-        n = gate_up_weight.size(1)
-        mm = masked_m if masked_m.dtype == torch.int32 else masked_m.to(torch.int32)
-        tiles, max_tiles = ops.build_tiles_masked(mm, m)
-        gateup_output = torch.empty((num_groups, m, n), device=dev, dtype=self.out_dtype)
-        ops.grouped_gemm(DisposibleTensor.maybe_unwrap(hidden_states_fp8[0]).view(num_groups * m, k),
-                         DisposibleTensor.maybe_unwrap(hidden_states_fp8[1]).view(num_groups * m, -1), gate_up_weight,
-                         gate_up_scale, tiles, max_tiles, _C.EPI_STORE, gateup_output.view(num_groups * m, n))
-        # the dispatch buffers are the largest tensors of the decode step: free them as early as the
-        # reference does (kernels already enqueued keep the memory alive through the caching allocator)
-        DisposibleTensor.maybe_dispose(hidden_states_fp8[0])
-        DisposibleTensor.maybe_dispose(hidden_states_fp8[1])
-        down_input = torch.empty((num_groups, m, n // 2), device=dev, dtype=gate_down_weight.dtype)
-        down_input_scale = torch.empty((num_groups, m, n // 2 // self.block_size), device=dev,
-                                       dtype=torch.float32)
-        silu_and_mul_masked_post_quant_fwd(gateup_output, down_input, down_input_scale, self.block_size, mm)
-        del gateup_output
-        n2 = gate_down_weight.size(1)
-        down_output = torch.empty((num_groups, m, n2), device=dev, dtype=self.out_dtype)
-        ops.grouped_gemm(down_input.view(num_groups * m, n // 2), down_input_scale.view(num_groups * m, -1),
-                         gate_down_weight, gate_down_scale, tiles, max_tiles, _C.EPI_STORE,
-                         down_output.view(num_groups * m, n2))
-        return down_output
-
-    def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,
-                up_weights: torch.Tensor, up_scale: torch.Tensor, down_weights: torch.Tensor,
-                down_scale: torch.Tensor, expert_list: List[int] = None):
-        if enable_moe_load_stats:
-            FusedMoELowLatency.recorder.record(topk_ids, self.layer_index, self.num_experts)
-        recv_hidden_states, topk_idx, topk_weights, masked_m, expected_m = self.token_dispatcher.dispatch(
-            hidden_states, topk_ids, topk_weights, self.num_experts)
-        out_states = self.experts(recv_hidden_states, up_weights, up_scale, down_weights, down_scale, masked_m,
-                                  expected_m)
-        return self.token_dispatcher.combine(out_states, topk_idx, topk_weights)
-
-    def wait(self, event):
-        event.current_stream_wait()
-
-    def dispatch_async(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, num_experts: Optional[int] = None,
-                       use_fp8: bool = True, async_finish: bool = True):
-        return self.token_dispatcher.dispatch_async(hidden_states, topk_idx, num_experts, use_fp8, async_finish)
-
-    def combine_async(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
-                      handle: tuple, async_finish: bool):
-        return self.token_dispatcher.combine_async(hidden_states, topk_idx, topk_weights, handle, async_finish)
-
-    def fusedmoe_forward(self, state, up_weight, up_scale, down_weight, down_scale):
-        hidden_shape = state["raw_hidden_shape"]
-        topk_idx = state["topk_idx"]
-        d = self.token_dispatcher
-        expected_m = (hidden_shape[0] * d.world_size * topk_idx.shape[1] + d.num_experts) // d.num_experts
-        return self.experts(state["recv_hidden_states"], up_weight, up_scale, down_weight, down_scale,
-                            state["recv_expert_count"], expected_m)
-
-
 def build_deepep_moe(low_latency_mode: bool, ep_size: int, ep_group: dist.ProcessGroup, num_experts: int,
                      hidden_dim: int, block_size: int, top_k: int, out_dtype: torch.dtype, layer_idx: int = 0,
                      chunk_size: Optional[int] = 32 * 1024, expert_alignment: int = 128):
@@ -231,48 +281,3 @@ def build_deepep_moe(low_latency_mode: bool, ep_size: int, ep_group: dist.Proces
     return FusedMoENormal(ep_size=ep_size, ep_group=ep_group, num_experts=num_experts, hidden_dim=hidden_dim,
                           layer_index=layer_idx, block_size=block_size, top_k=top_k, out_dtype=out_dtype,
                           chunk_size=chunk_size, expert_alignment=expert_alignment)
-
-
-class DlblasTritonFusedMoEBlockedF8Impl:
-    """Block-scaled FP8 fused MoE layer (ep_moe.py:413-484).  The name is the reference's; the kernels
-    underneath are the sm_100a CUDA extension."""
-
-    def __init__(self, top_k: int, num_experts: int, renormalize: bool = False, block_size: int = 128,
-                 out_dtype: torch.dtype = torch.float16, ep_size: int = 1):
-        self.num_experts = num_experts
-        self.top_k = top_k
-        self.renormalize = renormalize
-        self.block_size = block_size
-        self.out_dtype = out_dtype
-        self.ep_size = ep_size
-
-    def support_ep(self):
-        return True
-
-    def ep_expert_list(self, world_size: int, rank: int):
-        per_rank = (self.num_experts + world_size - 1) // world_size
-        first = rank * per_rank
-        return list(range(first, min(first + per_rank, self.num_experts)))
-
-    def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,
-                gate_up_weights: torch.Tensor, gate_up_scale: torch.Tensor, down_weights: torch.Tensor,
-                down_scale: torch.Tensor, expert_list: List[int] = None):
-        """hidden_states [..., H] bf16/fp16; topk_ids local to this rank's experts (-1 elsewhere) when
-        `expert_list` is a strict subset, and then shifted by expert_list[0] in place as the reference does."""
-        input_size = hidden_states.shape
-        hidden_states = hidden_states.flatten(0, -2)
-        expert_offset = 0
-        num_experts = None
-        if expert_list is not None and len(expert_list) != self.num_experts:
-            expert_offset = expert_list[0]
-            num_experts = self.num_experts
-        e_local = gate_up_weights.shape[0]
-        if num_experts is None:
-            num_experts = e_local * self.ep_size if self.ep_size > 1 else e_local
-        topk_weights = _renormalize(topk_weights, self.renormalize)
-        if expert_offset != 0:
-            topk_ids[topk_ids != -1] += expert_offset
-        output = moe_expert_forward(hidden_states, None, None, gate_up_weights, gate_up_scale, down_weights,
-                                    down_scale, topk_weights, topk_ids, self.top_k, hidden_states.dtype,
-                                    expert_offset, num_experts, _C.QUANT_RECIP_MUL, group_size=self.block_size)
-        return output.unflatten(0, input_size[:-1])

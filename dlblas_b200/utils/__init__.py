@@ -1,21 +1,16 @@
-"""`dlblas.utils` surface kept by this package (dlblas/utils/__init__.py:8-23 of the reference)."""
-from ..op_registry import op_registry
-from ..op_struct import OpImpl, OpParams
-from ..symbolic_var import SymVar, Tensor
-from .logger import get_logger
-from .utils import DisposibleTensor
+"""`dlblas.utils` surface kept by this package (dlblas/utils/__init__.py:8-23 of the reference):
+`register_dlblas_op`, `get_op`, `get_list_op_names`, `get_args_from_op_name`, all thin views of the one
+registry object, plus the symbolic argument types operators are registered with."""
+from ..op_registry import op_registry as _registry
+from ..op_struct import OpImpl, OpParams  # noqa: F401
+from ..symbolic_var import SymVar, Tensor  # noqa: F401
+from .logger import get_logger  # noqa: F401
+from .utils import DisposibleTensor  # noqa: F401
 
-register_dlblas_op = op_registry.register
+op_registry = _registry
 
-
-def get_list_op_names():
-    return op_registry.get_list_op_names()
-
-
-def get_args_from_op_name(name: str):
-    return op_registry.get_args_from_op_name(name)
-
-
-def get_op(name: str, args):
-    """Returns the OpImpl (callable) registered under `name` that matches `args`."""
-    return op_registry.get_op(name, args)
+# bound methods of the registry: same callables, same signatures as the reference's module-level functions
+register_dlblas_op = _registry.register
+get_list_op_names = _registry.get_list_op_names
+get_args_from_op_name = _registry.get_args_from_op_name
+get_op = _registry.get_op
