@@ -104,3 +104,27 @@ def test_disposible_tensor():
     assert d.shape == (2, 3)
     d.dispose()
     assert d.is_disposed and d.shape == (2, 3) and d.dtype == torch.float32
+
+
+def test_ctypes_signatures_have_the_header_arity():
+    """Every binding passes exactly as many arguments as the header declares."""
+    from dlblas_b200 import _C
+    hdr = open(os.path.join(ROOT, "include", "dlblas_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    decls = re.findall(r"DLB_API\s+[\w\s\*]+?\b(dlb_[a-z0-9_]+)\s*\(([^;]*?)\)\s*;", hdr, flags=re.S)
+    assert len(decls) == len(_C.SIGNATURES)
+    for name, params in decls:
+        params = params.strip()
+        n = 0 if params in ("", "void") else params.count(",") + 1
+        assert n == len(_C.SIGNATURES[name][1]), f"{name}: header has {n} parameters, binding {len(_C.SIGNATURES[name][1])}"
+
+
+def test_product_never_imports_the_oracle():
+    """The oracle is test infrastructure: nothing under the package (or the C sources) may refer to it."""
+    pkg = os.path.join(ROOT, "dlblas_b200")
+    for root, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(root, f)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), os.path.join(root, f)
+                assert "moe_oracle" not in text, os.path.join(root, f)
