@@ -36,15 +36,37 @@ def topk_gating(logits: Tensor, k: int, capacity_factor: float = 1.0, min_capaci
     return op(logits, k, capacity_factor, min_capacity, higher_precision)
 
 
+class _AliasFinder:
+    """Resolves `dlblas` and every `dlblas.<sub>` import to the module object of `dlblas_b200.<sub>`, so that
+    the two names share one module (one registry, one library handle, one set of module-level state)."""
+
+    def __init__(self, alias: str, target: str):
+        self.alias, self.target = alias, target
+
+    def find_spec(self, fullname, path=None, target=None):
+        if fullname != self.alias and not fullname.startswith(self.alias + "."):
+            return None
+        import importlib.machinery
+        return importlib.machinery.ModuleSpec(fullname, self)
+
+    def create_module(self, spec):
+        import importlib
+        module = importlib.import_module(self.target + spec.name[len(self.alias):])
+        self._specs = getattr(self, "_specs", {})
+        self._specs[id(module)] = getattr(module, "__spec__", None)
+        return module
+
+    def exec_module(self, module):
+        # already executed under its own name; the import system has just stamped the alias spec on it
+        original = getattr(self, "_specs", {}).pop(id(module), None)
+        if original is not None:
+            module.__spec__ = original
+
+
 def install_as_dlblas():
-    """Make `import dlblas` (and the sub-modules of this path) resolve to this package."""
-    import importlib
+    """Make `import dlblas` and `import dlblas.<anything on this path>` resolve to this package."""
     me = sys.modules[__name__]
+    if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):
+        sys.meta_path.insert(0, _AliasFinder("dlblas", __name__))
     sys.modules.setdefault("dlblas", me)
-    for sub in ("utils", "op_registry", "op_struct", "symbolic_var", "cache", "kernels", "kernels.fp8_gemm",
-                "kernels.fp8", "kernels.moe", "kernels.activation", "kernels.quant_dequant", "kernels.fused_moe_v3",
-                "kernels.topk_gating", "layers", "layers.moe", "layers.moe.ep_moe", "layers.moe.token_dispatcher",
-                "layers.moe.kernels", "layers.moe.kernels.fused_moe", "layers.moe.kernels.blocked_fp8_fused_moe",
-                "layers.moe.kernels.activation", "utils.logger", "utils.utils", "utils.device_utils"):
-        sys.modules.setdefault("dlblas." + sub, importlib.import_module(__name__ + "." + sub))
     return me
