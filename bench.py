@@ -84,6 +84,25 @@ def make_tokens(tokens: int, seed: int):
     return x, logits, bias
 
 
+def measured_traffic(kernel: str, experts: int):
+    """DRAM bytes per launch of `kernel` from the tracked table of ncu captures (dlblas_b200/ncu_traffic.json):
+    dram__bytes_read.sum + dram__bytes_write.sum of a small capture, scaled by the number of experts (the
+    weights dominate and every expert is streamed once).  An entry is used only while the kernel's source file
+    still has the hash it was captured with; otherwise the field is null rather than stale."""
+    import hashlib
+    path = os.path.join(ROOT, "dlblas_b200", "ncu_traffic.json")
+    if not os.path.exists(path):
+        return None, "no capture on record"
+    ent = json.load(open(path)).get(kernel)
+    if ent is None:
+        return None, "no capture on record"
+    src = os.path.join(ROOT, ent["source"])
+    digest = hashlib.sha256(open(src, "rb").read()).hexdigest()[:16]
+    if digest != ent["source_sha256_16"]:
+        return None, f"the capture on record predates the current {ent['source']}"
+    return ent["dram_bytes_per_launch"] * experts / ent["experts"], ent["note"]
+
+
 # --------------------------------------------------------------------------------------------
 # clocks
 # --------------------------------------------------------------------------------------------
@@ -147,14 +166,22 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------
 # reference arm: CPU restatement on the host cores
 # --------------------------------------------------------------------------------------------
-def cpu_sample(sample_tokens: int, w_cpu, x, logits, bias):
-    """One pass of the oracle over `sample_tokens` tokens of the workload; returns seconds."""
+def cpu_sample(rows, w_cpu, x, logits, bias, remap=None):
+    """One pass of the oracle over the tokens `rows` (an int = the first so many tokens, or an index tensor) of
+    the workload; returns (seconds, output).  `remap` renumbers global expert ids into the positions of a
+    reduced weight list (only the experts the sample hits)."""
     from oracle import moe_oracle as O
     w13, w13s, w2, w2s, sw13, sw13s, sw2, sw2s = w_cpu
-    xs, lg = x[:sample_tokens], logits[:sample_tokens]
+    if isinstance(rows, int):
+        rows = torch.arange(rows)
+    xs = x[rows]
     t0 = time.perf_counter()
-    w, ids = O.biased_grouped_topk(lg, bias, TOPK, True, GROUPS, TOPK_GROUP)
-    out = O.moe_layer(xs, w, ids.long(), w13, w13s, w2, w2s, top_k=TOPK)
+    # routing is decided on the whole batch's logits row by row, so a row's choice does not depend on the sample
+    w, ids = O.biased_grouped_topk(logits[rows], bias, TOPK, True, GROUPS, TOPK_GROUP)
+    ids = ids.long()
+    if remap is not None:
+        ids = remap[ids]
+    out = O.moe_layer(xs, w, ids, w13, w13s, w2, w2s, top_k=TOPK)
     out = out + O.dense_swiglu_mlp(xs, sw13, sw13s, sw2, sw2s)
     return time.perf_counter() - t0, out
 
@@ -363,69 +390,116 @@ def run_b200(args):
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(tmax[0]), float(tmax[1])
 
-    # ---- dominant kernel: the w13 grouped GEMM with the fused silu*up + quantisation epilogue ----
+    # ---- end-to-end ceiling: the step's host copies alone (same pinned buffers, same streams, no kernels) ----
+    def copies_only():
+        with torch.cuda.stream(h2d_stream):
+            in_bufs[0][0].copy_(x_pin, non_blocking=True)
+            in_bufs[0][1].copy_(logits_pin, non_blocking=True)
+        with torch.cuda.stream(d2h_stream):
+            out_pins[0].copy_(in_bufs[1][0], non_blocking=True)
+
+    for _ in range(2):
+        copies_only()
+    drain_e2e()
+    barrier()
+    ms_copy = time_steps(copies_only, max(args.steps, 5), dev, before_end=drain_e2e) / max(args.steps, 5)
+    barrier()
+    if world > 1:
+        tc = torch.tensor([ms_copy], dtype=torch.float64, device=dev)
+        dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+        ms_copy = float(tc[0])
+
+    # ---- dominant kernel: the w13 grouped GEMM with the fused silu*up + quantisation epilogue, on the rows this
+    # rank really works on (at N > 1: the receive buffer after a real dispatch, which every rank takes part in) ----
+    peaks = load_peaks()
+    e_loc = layer.e_local + (1 if world == 1 else 0)
+    w13, w13s, w2, w2s = layer.weights
+    w_r, ids_r = ops.route_grouped_topk(logits_d, bias_d, TOPK, True, GROUPS, TOPK_GROUP)
+    if world == 1:
+        ids_k = torch.cat([ids_r.long(), layer.shared_col_ids[:tokens]], dim=1)
+        s_rows = tokens * (TOPK + 1)
+        sidx, st, en, pos = ops.sort_by_expert(ids_k, e_loc, want_pos=True)
+        a1, a1s = ops.quant_fp8(x_d, 128, _C.QUANT_RECIP_MUL, 0.0, False, pos, TOPK + 1, s_rows)
+    else:
+        disp = layer.ep.p2p_dispatcher
+        assert disp is not None, "the roofline leg times the peer-to-peer exchange's receive buffer"
+        (rq, rs), ids_k, _rw = disp.dispatch_from_hidden(x_d, ids_r.long(), w_r, 128)
+        s_rows = ids_k.numel()
+        sidx, st, en, pos = ops.sort_by_expert(ids_k, e_loc, want_pos=True)
+        a1, a1s = ops.permute_rows(rq, rs.contiguous(), pos, TOPK, s_rows)
+    mt = ops.max_tiles_for(s_rows, e_loc)
+    tiles = ops.build_tiles(st, en, 0, e_loc, mt)
+    hq = torch.empty(s_rows, INTER, dtype=FP8, device=dev)
+    hs = torch.empty(s_rows, INTER // 128, dtype=torch.float32, device=dev)
+    routed_rows = int((ids_k >= 0).sum())
+    tile_rows_issued = int(tiles[0]) * 128
+
+    def gemm1():
+        ops.grouped_gemm(a1, a1s, w13[:e_loc], w13s[:e_loc], tiles, mt, _C.EPI_SWIGLU_QUANT, hq, q_scale=hs,
+                         round_dtype=torch.bfloat16)
+
+    for _ in range(3):
+        gemm1()
+    n_roof = max(args.steps, 5)
+    kms = time_steps(gemm1, n_roof, dev) / n_roof
+    _C.check_status(dev)
     roof = None
     cpu_base = None
+    parity = None
     if rank == 0:
-        peaks = load_peaks()
-        e_loc = layer.e_local + (1 if world == 1 else 0)
-        w13, w13s, w2, w2s = layer.weights
-        w_r, ids_r = ops.route_grouped_topk(logits_d, bias_d, TOPK, True, GROUPS, TOPK_GROUP)
-        if world == 1:
-            ids_k = torch.cat([ids_r.long(), layer.shared_col_ids[:tokens]], dim=1)
-            k_eff = TOPK + 1
-        else:
-            # single-rank stand-in for the received tokens: this rank's share of the routed slots
-            mine = (ids_r >= rank * layer.e_local) & (ids_r < (rank + 1) * layer.e_local)
-            ids_k = torch.where(mine, ids_r - rank * layer.e_local, torch.full_like(ids_r, -1)).long()
-            k_eff = TOPK
-        s_rows = tokens * k_eff
-        sidx, st, en, pos = ops.sort_by_expert(ids_k, e_loc, want_pos=True)
-        mt = ops.max_tiles_for(s_rows, e_loc)
-        tiles = ops.build_tiles(st, en, 0, e_loc, mt)
-        a1, a1s = ops.quant_fp8(x_d, 128, _C.QUANT_RECIP_MUL, 0.0, False, pos, k_eff, s_rows)
-        hq = torch.empty(s_rows, INTER, dtype=FP8, device=dev)
-        hs = torch.empty(s_rows, INTER // 128, dtype=torch.float32, device=dev)
-        routed_rows = int((ids_k >= 0).sum())
-
-        def gemm1():
-            ops.grouped_gemm(a1, a1s, w13[:e_loc], w13s[:e_loc], tiles, mt, _C.EPI_SWIGLU_QUANT, hq, q_scale=hs,
-                             round_dtype=torch.bfloat16)
-
-        for _ in range(3):
-            gemm1()
-        kms = time_steps(gemm1, max(args.steps, 5), dev) / max(args.steps, 5)
         flops = 2.0 * routed_rows * (2 * INTER) * H
         achieved = flops / (kms * 1e-3) / 1e12
         # a long back-to-back loop of this kernel runs under the power cap like the step itself:
         # compare it with the sustained figure; a short loop with the burst figure
-        n_roof = max(args.steps, 5)
-        sustained = kms * n_roof > 100.0
+        sustained = kms * n_roof > 1000.0
         bf16_peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
         fp8_peak = 2.0 * bf16_peak
-        # DRAM traffic per launch: dram__bytes_read + write of one ncu capture of this kernel on 32 experts x
-        # 256 rows (1.166 GB, profiles/gemm_fp8_w13_grouped_32experts.md), scaled by the number of experts;
-        # weights dominate the traffic and every expert is streamed once, so it grows in proportion
-        traffic = 1.166e9 * e_loc / 32.0
-        roof = {"kernel": "gemm_fp8_kernel<256, SWIGLU_QUANT> (w13 grouped GEMM)", "bound": "tensor",
+        traffic, traffic_note = measured_traffic("gemm_fp8_w13_grouped", e_loc)
+        roof = {"kernel": "gemm_fp8 w13 grouped GEMM with the silu*up + quantise epilogue", "bound": "tensor",
                 "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
                 "traffic": traffic, "ms_per_launch": kms, "launches_timed": n_roof,
+                "rows": routed_rows, "tile_fill": routed_rows / max(tile_rows_issued, 1),
+                "rows_note": "the rows of the step itself" if world == 1 else
+                             "this rank's receive buffer after a real dispatch of the step's tokens",
                 "peak_note": f"2 x {peaks['source']} cuBLAS bf16 {'sustained' if sustained else 'burst'} figure "
                              f"({bf16_peak} TFLOP/s): e4m3 tensor rate is twice bf16 on B200; no FP8 figure is "
                              f"measured on this pool",
-                "traffic_note": "ncu dram bytes of a 32-expert capture scaled by experts/32"}
-        if not args.no_cpu:
+                "traffic_note": traffic_note}
+
+    # ---- parity of the timed configuration: rows of a full-batch step against the CPU oracle ----
+    if not args.no_cpu:
+        from oracle import moe_oracle as O
+        full_out = layer.step(x_d, logits_d, bias_d)           # every rank: the step has collectives
+        _C.check_status(dev)
+        if rank == 0:
             torch.set_num_threads(os.cpu_count() or 1)
-            if world == 1:
-                w_cpu = [w13[:E].cpu(), w13s[:E].cpu(), w2[:E].cpu(), w2s[:E].cpu(), w13[E].cpu(), w13s[E].cpu(),
-                         w2[E].cpu(), w2s[E].cpu()]
-                dt, ref_out = cpu_sample(args.cpu_tokens, w_cpu, x_h, logits_h, bias_h)
-                got = layer.step(x_d[:args.cpu_tokens].contiguous(), logits_d[:args.cpu_tokens].contiguous(), bias_d)
-                from oracle import moe_oracle as O
-                err = O.rel_frobenius(got.cpu(), ref_out)
-                cpu_base = {"value": args.cpu_tokens / dt, "unit": "tokens/s", "cores": torch.get_num_threads(),
-                            "kind": "port", "sample": f"first {args.cpu_tokens} tokens of the step's batch, all "
-                            f"experts they hit, through oracle/moe_oracle.py", "rel_frobenius_vs_gpu": err}
+            n_s = max(args.cpu_tokens, 1)
+            rows = torch.unique(torch.linspace(0, tokens - 1, n_s).long())
+            _, ids_o = O.biased_grouped_topk(logits_h[rows], bias_h, TOPK, True, GROUPS, TOPK_GROUP)
+            assert torch.equal(ids_o, ids_r.cpu()[rows]), "routing ids of the sampled rows differ from the oracle"
+            hit = torch.unique(ids_o.long())
+            remap = torch.full((E,), -1, dtype=torch.int64)
+            remap[hit] = torch.arange(hit.numel())
+            nl = layer.e_local
+            parts = {k_: [] for k_ in range(4)}
+            for r in range(world):                              # weights of rank r: seeded, regenerated here
+                mine = hit[(hit >= r * nl) & (hit < (r + 1) * nl)] - r * nl
+                if mine.numel() == 0:
+                    continue
+                wr = layer.weights if r == rank else make_weights(nl + 1, 1000 + r, dev)
+                for k_ in range(4):
+                    parts[k_].append(wr[k_][mine.to(dev)].cpu())
+                del wr
+            w_cpu = [torch.cat(parts[k_]) for k_ in range(4)] + [w13[nl].cpu(), w13s[nl].cpu(), w2[nl].cpu(),
+                                                                 w2s[nl].cpu()]
+            dt, ref_out = cpu_sample(rows, w_cpu, x_h, logits_h, bias_h, remap)
+            err = O.rel_frobenius(full_out[rows.to(dev)].cpu(), ref_out)
+            sample = (f"{rows.numel()} rows spread over the step's batch of {tokens} tokens, taken from the output "
+                      f"of the full-batch step, all {hit.numel()} experts they hit, through oracle/moe_oracle.py")
+            cpu_base = {"value": rows.numel() / dt, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                        "kind": "port", "sample": sample, "rel_frobenius_vs_gpu": err}
+            parity = {"rel_frobenius_vs_oracle": err, "rows": int(rows.numel()), "routing_ids_equal": True,
+                      "tolerance": 2e-2}
     if world > 1:
         dist.barrier()
     if rank == 0:
@@ -442,13 +516,22 @@ def run_b200(args):
                        "parallelism": f"ep{world}",
                        "l2": "inputs larger than L2: every step streams this rank's expert weights "
                              f"({(layer.e_local + 1) * 3 * H * INTER / 1e9:.2f} GB) from HBM"},
-            "tflops": tflops, "fp8_peak_frac": tflops / (2.0 * load_peaks()["bf16_tflops_sustained"] * world),
+            "tflops": tflops,
+            "fp8_peak_frac": tflops / (2.0 * load_peaks()["bf16_tflops_sustained" if ms > 1000.0 else "bf16_tflops"]
+                                       * world),
+            "fp8_peak_note": "layer TFLOP/s over 2 x the measured bf16 figure (sustained for a timed region longer "
+                             "than 1 s, else burst)",
             "e2e": {"value": tps_e2e, "unit": "tokens/s", "h2d_bytes_per_step": tokens * H * 2 + tokens * E * 4,
-                    "d2h_bytes_per_step": tokens * H * 2, "ms_per_step": ms_e2e / args.steps},
+                    "d2h_bytes_per_step": tokens * H * 2, "ms_per_step": ms_e2e / args.steps,
+                    "host_copy_ceiling_ms": ms_copy,
+                    "host_copy_note": "the same copies (pinned host <-> device, both directions at once, every rank "
+                                      "at the same time) with no kernel running: the floor of an end-to-end step on "
+                                      "this box"},
             "gpu_launches": launches, "clocks": clocks, "roofline": roof,
         }
         if cpu_base is not None:
             line["cpu_baseline"] = cpu_base
+            line["parity"] = parity
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -508,6 +591,118 @@ def run_profile(args):
                                  round_dtype=torch.bfloat16)
             ops.grouped_gemm(hq, hs, w2, w2s, tiles, mt, _C.EPI_SCATTER_WEIGHT, y, sorted_idx=sidx, weights=wts)
     torch.cuda.synchronize()
+    _C.check_status(dev)
+
+
+def _time_kernel(fn, dev, iters=20, flush=None):
+    """Average CUDA-event time of one launch in ms; `flush` (a buffer larger than L2) is rewritten between
+    launches so that every launch starts from a cold L2."""
+    for _ in range(3):
+        fn()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize(dev)
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def run_profile_bandwidth(args):
+    """`--profile bandwidth`: every HBM-bound kernel of the step alone at the step's sizes, CUDA events around
+    each launch, L2 flushed in between; prints a markdown table of algorithmic bytes, time, GB/s and the fraction
+    of the measured copy bandwidth."""
+    from dlblas_b200 import _C, ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak = load_peaks()["hbm_gbs"]
+    t, k = args.tokens, TOPK + 1
+    x_h, logits_h, bias_h = make_tokens(t, 100)
+    x, logits, bias = x_h.to(dev), logits_h.to(dev), bias_h.to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    w, ids = ops.route_grouped_topk(logits, bias, TOPK, True, GROUPS, TOPK_GROUP)
+    ids9 = torch.cat([ids.long(), torch.full((t, 1), E, dtype=torch.int64, device=dev)], dim=1)
+    s_rows = t * k
+    sidx, st, en, pos = ops.sort_by_expert(ids9, E + 1, want_pos=True)
+    y = torch.randn(s_rows, H, device=dev).to(torch.bfloat16)
+    gu = torch.randn(s_rows // 4, 2 * INTER, device=dev).to(torch.bfloat16)
+    rows = []
+
+    def add(name, fn, nbytes):
+        ms = _time_kernel(fn, dev, 20, flush)
+        gbs = nbytes / ms / 1e6
+        rows.append(f"| {name} | {nbytes / 1e6:.1f} | {ms * 1e3:.1f} | {gbs:.0f} | {gbs / peak:.2f} |")
+
+    add("grouped_topk (8192 x 256 fp32 logits -> ids, weights)", lambda: ops.route_grouped_topk(
+        logits, bias, TOPK, True, GROUPS, TOPK_GROUP), 4.0 * t * E + 8.0 * t * TOPK)
+    add("sort_by_expert (73 728 slots, 257 experts; 4 kernels)", lambda: ops.sort_by_expert(
+        ids9, E + 1, want_pos=True), 8.0 * s_rows * 2 + 12.0 * s_rows + 16.0 * (E + 1))
+    add("quant_fp8, fan-out 9 (x bf16 -> a1 e4m3 + scales in expert order)", lambda: ops.quant_fp8(
+        x, 128, _C.QUANT_RECIP_MUL, 0.0, False, pos, k, s_rows), 2.0 * t * H + k * t * H * (1 + 4 / 128))
+    add("quant_fp8, no fan-out", lambda: ops.quant_fp8(x, 128, _C.QUANT_RECIP_MUL, 0.0),
+        2.0 * t * H + t * H * (1 + 4 / 128))
+    add("silu_mul_quant (18 432 x 4096 bf16 -> e4m3 + scales)", lambda: ops.silu_mul_quant(
+        gu, _C.QUANT_RECIP_MUL, 0.0), 4.0 * gu.shape[0] * INTER + gu.shape[0] * INTER * (1 + 4 / 128))
+    add("sum_topk (73 728 x 7168 bf16 -> 8192 x 7168)", lambda: ops.sum_topk(y, t, k, ids9, 0, E + 1),
+        2.0 * s_rows * H + 2.0 * t * H)
+    print(f"HBM copy bandwidth measured on this pool: {peak:.0f} GB/s\n")
+    print("| kernel | algorithmic MB | us / launch | GB/s | of measured |\n|---|---|---|---|---|")
+    print("\n".join(rows))
+
+
+def run_profile_sweep(args):
+    """`--profile sweep`: the stand-alone block-scaled GEMM over the 12 shapes of the benchmark set, and the two
+    grouped GEMMs of the Mixtral-shaped layer; CUDA events, L2 flushed between launches."""
+    from dlblas_b200 import _C, ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device=dev).manual_seed(3)
+    print(f"divisor: 2 x {peaks['source']} cuBLAS bf16 burst figure = {fp8_peak:.0f} TFLOP/s\n")
+    print("| M | N | K | us / launch | TFLOP/s | of 2 x bf16 burst |\n|---|---|---|---|---|---|")
+    for m in (128, 1024, 4096, 8192):
+        for n, k in ((24576, 1536), (7168, 2048), (4096, 7168)):
+            a = torch.randn(m, k, generator=g, device=dev).to(FP8)
+            b = torch.randn(n, k, generator=g, device=dev).to(FP8)
+            a_s = torch.rand(m, k // 128, generator=g, device=dev)
+            b_s = torch.rand(n // 128, k // 128, generator=g, device=dev)
+            ms = _time_kernel(lambda: ops.fp8_gemm(a, b, a_s, b_s, torch.bfloat16), dev, 10, flush)
+            tf = 2.0 * m * n * k / ms / 1e9
+            print(f"| {m} | {n} | {k} | {ms * 1e3:.1f} | {tf:.0f} | {tf / fp8_peak:.2f} |")
+    # Mixtral-shaped layer: 4096 tokens, top-2 of 8 experts, hidden 4096, intermediate 14336
+    t, h, inter, e, k = 4096, 4096, 14336, 8, 2
+    ws = []
+    for shape in ((e, 2 * inter, h), (e, h, inter)):
+        wq = torch.empty(shape, dtype=FP8, device=dev)
+        wsc = torch.empty(shape[0], shape[1] // 128, shape[2] // 128, device=dev)
+        for i in range(e):
+            q, sc = quantize_blocks_gpu(torch.randn(1, shape[1], shape[2], generator=g, device=dev) * 0.02)
+            wq[i], wsc[i] = q[0], sc[0]
+        ws += [wq, wsc]
+    x = torch.randn(t, h, generator=g, device=dev).to(torch.bfloat16)
+    wt, ids = ops.route_softmax_topk(torch.randn(t, e, generator=g, device=dev), k, True)
+    sidx, st, en, pos = ops.sort_by_expert(ids, e, want_pos=True)
+    mt = ops.max_tiles_for(t * k, e)
+    tiles = ops.build_tiles(st, en, 0, e, mt)
+    a1, a1s = ops.quant_fp8(x, 128, _C.QUANT_RECIP_MUL, 0.0, False, pos, k, t * k)
+    hq = torch.empty(t * k, inter, dtype=FP8, device=dev)
+    hs = torch.empty(t * k, inter // 128, dtype=torch.float32, device=dev)
+    y = torch.empty(t * k, h, dtype=torch.bfloat16, device=dev)
+    ms1 = _time_kernel(lambda: ops.grouped_gemm(a1, a1s, ws[0], ws[1], tiles, mt, _C.EPI_SWIGLU_QUANT, hq, q_scale=hs,
+                                                round_dtype=torch.bfloat16), dev, 10, flush)
+    ms2 = _time_kernel(lambda: ops.grouped_gemm(hq, hs, ws[2], ws[3], tiles, mt, _C.EPI_SCATTER_WEIGHT, y,
+                                                sorted_idx=sidx, weights=wt.flatten()), dev, 10, flush)
+    f1, f2 = 2.0 * t * k * 2 * inter * h, 2.0 * t * k * inter * h
+    print("\nMixtral-shaped layer (4096 tokens, 8 experts top-2, hidden 4096, intermediate 14336), grouped GEMMs:\n")
+    print("| GEMM | us / launch | TFLOP/s | of 2 x bf16 burst |\n|---|---|---|---|")
+    print(f"| w13 + silu*up + quantise | {ms1 * 1e3:.1f} | {f1 / ms1 / 1e9:.0f} | {f1 / ms1 / 1e9 / fp8_peak:.2f} |")
+    print(f"| w2 + routed weight, scattered | {ms2 * 1e3:.1f} | {f2 / ms2 / 1e9:.0f} | {f2 / ms2 / 1e9 / fp8_peak:.2f} |")
     _C.check_status(dev)
 
 
@@ -598,7 +793,7 @@ def run_decode(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile", default="", choices=["", "gemm1", "gemm2", "dense", "gemm16"],
+    ap.add_argument("--profile", default="", choices=["", "gemm1", "gemm2", "dense", "gemm16", "bandwidth", "sweep"],
                     help="run only one kernel on a small case (for ncu) and exit")
     ap.add_argument("--experts", type=int, default=32, help="experts of the --profile case")
     ap.add_argument("--gpus", type=int, default=1)
@@ -611,7 +806,11 @@ def main():
     ap.add_argument("--workload", default="prefill", choices=["prefill", "decode"],
                     help="prefill = the headline benchmark; decode = 128 tokens per GPU, latency percentiles")
     args = ap.parse_args()
-    if args.profile:
+    if args.profile == "bandwidth":
+        run_profile_bandwidth(args)
+    elif args.profile == "sweep":
+        run_profile_sweep(args)
+    elif args.profile:
         run_profile(args)
     elif args.workload == "decode" and args.impl == "b200":
         run_decode(args)

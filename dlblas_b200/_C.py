@@ -30,6 +30,7 @@ SIGNATURES = {
     "dlb_version": (c_int, []),
     "dlb_last_error_string": (ctypes.c_char_p, []),
     "dlb_launch_count": (c_i64, [c_int]),
+    "dlb_set_wait_policy": (c_int, [ctypes.c_uint64, c_int]),
     "dlb_sort_by_expert_workspace_size": (c_sz, [c_i64, c_int]),
     "dlb_sort_by_expert": (c_int, [c_vp, c_int, c_i64, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "dlb_sort_by_expert_static_capacity": (c_sz, []),
@@ -55,6 +56,7 @@ SIGNATURES = {
     "dlb_p2p_unpack_meta": (c_int, [c_vp, c_int, c_int, c_vp, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
     "dlb_p2p_sum_push": (c_int, [c_vp, c_int, c_vp, c_int, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
     "dlb_p2p_push_rows": (c_int, [c_vp, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
+    "dlb_p2p_barrier": (c_int, [c_vp, c_int, c_int, ctypes.c_uint32, ctypes.c_uint64, c_vp, c_vp]),
     "dlb_grouped_gemm_16bit": (c_int, [c_vp, c_vp, c_int, c_i64, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_vp, c_i64,
                                        c_vp, c_vp]),
     "dlb_moe_build_tiles_rows": (c_int, [c_vp, c_vp, c_int, c_int, c_int, c_vp, c_int, c_vp]),
@@ -142,6 +144,20 @@ def check_status(device=None):
     if v != 0:
         w.zero_()
         raise RuntimeError(f"dlblas_b200: a GEMM kernel gave up waiting on a barrier (status {v})")
+
+
+def maybe_check_status(device=None):
+    """The layers call this at the end of every forward.  With DLBLAS_CHECK_STATUS=1 it synchronises and raises
+    if a bounded wait gave up during the call (at the price of one host synchronisation per layer); by default
+    it does nothing and the caller is expected to run `check_status()` at a point of its own choosing."""
+    if os.environ.get("DLBLAS_CHECK_STATUS", "0") == "1":
+        check_status(device)
+
+
+def set_wait_policy(limit_cycles: int = 0, withhold_loads: bool = False):
+    """Limit of one barrier wait inside the GEMM kernels in SM clock cycles (0 = default, about 2 s);
+    `withhold_loads` is the self-test switch of dlb_set_wait_policy."""
+    check(lib().dlb_set_wait_policy(int(limit_cycles), 1 if withhold_loads else 0))
 
 
 def launch_count(reset=False) -> int:

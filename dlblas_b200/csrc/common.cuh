@@ -22,6 +22,9 @@ inline int check_cuda(cudaError_t e, const char* what) {
 
 int sm_count();  // multiprocessors of the current device (cached per device)
 void count_launch();  // bumps the per-thread kernel launch counter read by dlb_launch_count()
+// limit of one barrier wait in SM clock cycles: the value given to dlb_set_wait_policy(), else `fallback`
+unsigned long long wait_limit_cycles(unsigned long long fallback);
+bool withhold_loads();  // dlb_set_wait_policy(): the GEMMs' load role issues nothing (makes the waits run out)
 
 #define DLB_CHECK_LAUNCH(name)                                  \
   do {                                                          \
@@ -59,10 +62,16 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
-// Two fp32 -> packed e4m3x2 (lo in bits 0-7), round to nearest even, saturating to +-448.
+// The reference clamps before it casts (`tl.clamp(out, fp8_min, fp8_max)`, dlblas/kernels/moe.py:413,
+// dlblas/kernels/fp8.py:48): min(max(x, -448), 448) with the non-propagating min / max of the GPU, so a NaN
+// (0 / 0 of an all-zero group whose scale is 0) becomes -448 and never reaches the payload.  fmaxf / fminf
+// return the non-NaN operand, which reproduces that.
+__device__ __forceinline__ float clamp_e4m3(float x) { return fminf(fmaxf(x, -448.f), 448.f); }
+
+// Two fp32 -> packed e4m3x2 (lo in bits 0-7): clamp to +-448, then round to nearest even.
 __device__ __forceinline__ uint16_t f32x2_to_e4m3x2(float lo, float hi) {
   uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(clamp_e4m3(hi)), "f"(clamp_e4m3(lo)));
   return r;
 }
 

@@ -439,7 +439,7 @@ extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, i
   g.num_n_tiles = (int)ceil_div(n, (int64_t)BN);
   g.idesc = make_idesc16(dtype == DLB_BF16 ? 1u : 0u, ctas);
   g.status = status;
-  g.timeout_cycles = DEFAULT_TIMEOUT_CYCLES;
+  g.timeout_cycles = wait_limit_cycles(DEFAULT_TIMEOUT_CYCLES);
   const int workers = sm_count() / ctas;
   const long long total = (long long)(tiles != nullptr ? max_tiles : g.num_m_tiles_static) * g.num_n_tiles;
   const int grid = ctas * (int)(total < workers ? total : workers);

@@ -70,6 +70,7 @@ struct GemmArgs {
   const float* weights;
   int* status;
   unsigned long long timeout_cycles;
+  int withhold_loads;         // self-test of the time-out path: the producer issues no load
 };
 
 // kind::f8f6f4, A and B e4m3 K-major, fp32 accumulate, M = 128, N = bn.
@@ -259,7 +260,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-          if constexpr (PAIR) {
+          if (g.withhold_loads) {
+            // nothing is loaded: the consumers' waits run into their limit
+          } else if constexpr (PAIR) {
             // each CTA fetches its 128 rows of A and its half of the B tile (the gate slab in the leader, the up
             // slab in its partner for the fused w13 epilogue); all of it is counted on the leader's barrier
             const uint32_t lead_full = mapa(full_bar(s), 0);
@@ -286,7 +289,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           __syncwarp();
         }
       }
-      if (!ok) {
+      if (!ok && !g.withhold_loads) {
         // drain: give the loads of the last STAGES iterations a bounded chance to land
         const uint32_t first = it > (uint32_t)C::STAGES ? it - C::STAGES : 0u;
         for (uint32_t i = first; i < it; ++i)
@@ -451,7 +454,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const Tile ti = decode_tile<BN, MODE, CTAS>(g, t, (int)rank);
       const bool row_ok = r < ti.rows;
       const long long p = (long long)ti.row0 + r;          // row of A / sorted position
-      const float* as_ptr = g.a_s + (row_ok ? p : (long long)ti.row0) * g.a_s_rs;
+      // threads without a row read the scales of a row that exists (a pair's second CTA can hold an empty
+      // half tile whose first row lies beyond the end of A)
+      const float* as_ptr = g.a_s + (row_ok ? p : (long long)min(ti.row0, g.m - 1)) * g.a_s_rs;
       // scale blocks of the two segments
       const float* bs_ptr[2];
       {
@@ -747,7 +752,8 @@ extern "C" int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int6
   g.num_m_tiles_static = m_tiles;
   g.num_n_tiles = (int)ceil_div(n, bn);
   g.status = status;
-  g.timeout_cycles = DEFAULT_TIMEOUT_CYCLES;
+  g.timeout_cycles = wait_limit_cycles(DEFAULT_TIMEOUT_CYCLES);
+  g.withhold_loads = withhold_loads() ? 1 : 0;
   const long long total = (long long)m_tiles * g.num_n_tiles;
   const int workers = sms / ctas;
   const int grid = ctas * (int)(total < workers ? total : workers);
@@ -796,7 +802,8 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t row
   g.sorted_idx = reinterpret_cast<const long long*>(sorted_idx);
   g.weights = weights;
   g.status = status;
-  g.timeout_cycles = DEFAULT_TIMEOUT_CYCLES;
+  g.timeout_cycles = wait_limit_cycles(DEFAULT_TIMEOUT_CYCLES);
+  g.withhold_loads = withhold_loads() ? 1 : 0;
   DLB_REQUIRE(tile_rows == 128 || tile_rows == 256, DLB_ERR_INVALID, "grouped_gemm: tile_rows must be 128 or 256");
   const int ctas = tile_rows / BM;
   int bn = 256;

@@ -175,6 +175,35 @@ __global__ void __launch_bounds__(THREADS) sum_push_kernel(const T* __restrict__
   }
 }
 
+// Barrier among the ranks of an expert-parallel group, one rank per GPU.  Rank i owns an array of one 32-bit
+// word per peer; arriving means storing the barrier's number (a counter that every rank advances in step) into
+// word "my rank" of every peer's array with release semantics at system scope, so that everything this rank
+// stored into the peers' memory before, from earlier kernels of the stream included, is visible to a peer that
+// has seen the number.  Then thread r waits until word r of the own array has reached the number.  The wait is
+// bounded: when `limit_ns` nanoseconds have passed the kernel records DLB_STATUS_TIMEOUT in the status word and
+// returns; it never traps and never spins without a limit, so a rank that died or raised before its arrival
+// costs its peers one time-out and an exception on the host, not a hung GPU.  Plain peer stores and loads only.
+__global__ void __launch_bounds__(32) rank_barrier_kernel(PeerPtrs signals, int world, int my_rank, uint32_t number,
+                                                          unsigned long long limit_ns, int* __restrict__ status) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  uint32_t* theirs = reinterpret_cast<uint32_t*>(signals.p[r]) + my_rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(number) : "memory");
+  const uint32_t* mine = reinterpret_cast<const uint32_t*>(signals.p[my_rank]) + r;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    if ((int32_t)(seen - number) >= 0) break;
+    if (globaltimer_ns() - t0 > limit_ns) {
+      if (status != nullptr) atomicExch(status, DLB_STATUS_TIMEOUT);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
 int grid_for(long long total_threads) {
   long long blocks = ceil_div(total_threads, THREADS);
   const long long cap = (long long)sm_count() * 16;
@@ -292,5 +321,22 @@ extern "C" int dlb_p2p_sum_push(const void* y, int dtype, const int64_t* ids, in
                                                      my_rank, region_rows, pd);
   count_launch();
   DLB_CHECK_LAUNCH("sum_push_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_p2p_barrier(const void* const* peer_signals, int world, int my_rank, uint32_t number,
+                               uint64_t limit_ns, int32_t* status, void* stream) {
+  DLB_REQUIRE(world > 0 && world <= MAX_WORLD && my_rank >= 0 && my_rank < world, DLB_ERR_INVALID,
+              "p2p_barrier: world=%d (max %d), rank=%d", world, MAX_WORLD, my_rank);
+  DLB_REQUIRE(limit_ns > 0, DLB_ERR_INVALID, "p2p_barrier: the wait needs a limit");
+  PeerPtrs ps;
+  for (int r = 0; r < world; ++r) {
+    DLB_REQUIRE(peer_signals != nullptr && peer_signals[r] != nullptr && (uintptr_t)peer_signals[r] % 4 == 0,
+                DLB_ERR_INVALID, "p2p_barrier: bad signal pointer for rank %d", r);
+    ps.p[r] = const_cast<void*>(peer_signals[r]);
+  }
+  rank_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ps, world, my_rank, number, limit_ns, status);
+  count_launch();
+  DLB_CHECK_LAUNCH("rank_barrier_kernel");
   return DLB_OK;
 }

@@ -93,6 +93,41 @@ __global__ void __launch_bounds__(WARPS * 32) softmax_topk_kernel(const T* __res
   }
 }
 
+// Logistic function whose result does not depend on any library's exponential: evaluated in fp64 with
+// individually rounded IEEE operations only (no fused multiply-add, no transcendental call) and rounded
+// once to fp32, so that a restatement with the same sequence of operations on any IEEE machine gives the
+// same bits.  exp(z), z = -x: n = rint(z * log2(e)), r = z - n * ln2 (two-part constant),
+// degree-13 Taylor polynomial in r (|r| <= 0.35: truncation below 1e-17), scaled by 2^n in two exact steps.
+// The score differs from a correctly rounded fp32 sigmoid in well under one input in a million, and from
+// torch's fp32 sigmoid by at most one unit in the last place.
+__device__ __forceinline__ double pow2_exact(int n) { return __longlong_as_double((long long)(n + 1023) << 52); }
+
+__device__ __forceinline__ float sigmoid_exact(float x) {
+  double z = -(double)x;
+  z = fmin(fmax(z, -750.0), 750.0);
+  const double n = rint(__dmul_rn(z, 1.4426950408889634));
+  double r = __dsub_rn(z, __dmul_rn(n, 0.6931471803691238));
+  r = __dsub_rn(r, __dmul_rn(n, 1.9082149292705877e-10));
+  double p = 1.6059043836821613e-10;
+  p = __dadd_rn(__dmul_rn(p, r), 2.08767569878681e-09);
+  p = __dadd_rn(__dmul_rn(p, r), 2.505210838544172e-08);
+  p = __dadd_rn(__dmul_rn(p, r), 2.755731922398589e-07);
+  p = __dadd_rn(__dmul_rn(p, r), 2.7557319223985893e-06);
+  p = __dadd_rn(__dmul_rn(p, r), 2.48015873015873e-05);
+  p = __dadd_rn(__dmul_rn(p, r), 0.0001984126984126984);
+  p = __dadd_rn(__dmul_rn(p, r), 0.001388888888888889);
+  p = __dadd_rn(__dmul_rn(p, r), 0.008333333333333333);
+  p = __dadd_rn(__dmul_rn(p, r), 0.041666666666666664);
+  p = __dadd_rn(__dmul_rn(p, r), 0.16666666666666666);
+  p = __dadd_rn(__dmul_rn(p, r), 0.5);
+  p = __dadd_rn(__dmul_rn(p, r), 1.0);
+  p = __dadd_rn(__dmul_rn(p, r), 1.0);
+  const int ni = (int)n;              // |n| <= 1083
+  const int n1 = ni / 2, n2 = ni - n1;  // both powers of two are normal numbers
+  const double e = __dmul_rn(__dmul_rn(p, pow2_exact(n1)), pow2_exact(n2));
+  return __double2float_rn(__ddiv_rn(1.0, __dadd_rn(1.0, e)));
+}
+
 // DeepSeek-V3 style grouped routing (dlblas/kernels/moe.py:477-521).
 template <typename T, int VPT>
 __global__ void __launch_bounds__(WARPS * 32) grouped_topk_kernel(const T* __restrict__ logits,
@@ -113,7 +148,7 @@ __global__ void __launch_bounds__(WARPS * 32) grouped_topk_kernel(const T* __res
     for (int s = 0; s < VPT; ++s) {
       const int e = s * 32 + lane;
       if (e < experts) {
-        sc[s] = 1.f / (1.f + expf(-x[s]));
+        sc[s] = sigmoid_exact(x[s]);
         ch[s] = sc[s] + __ldg(bias + e);
       } else {
         sc[s] = 0.f;

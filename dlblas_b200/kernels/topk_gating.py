@@ -1,6 +1,7 @@
 """`dlblas.topk_gating` (dlblas/kernels/topk_gating.py:245-317 of the reference), forward and backward:
 capacity-limited softmax top-k gating, registered with the op registry under 'topk_gating'."""
 import math
+import struct
 
 import torch
 
@@ -11,10 +12,14 @@ from ..utils import register_dlblas_op
 
 
 def _capacity(num_tokens: int, num_experts: int, capacity_factor: float, min_capacity: int) -> int:
-    """ceil(T / E * capacity_factor), at least min_capacity (topk_gating.py:15-24), computed on the
-    host from the shape: no device round trip."""
-    cap = int(math.ceil((num_tokens / num_experts) * capacity_factor))
-    return max(cap, int(min_capacity))
+    """ceil(T / E * capacity_factor), at least min_capacity (topk_gating.py:15-24), computed on the host from the
+    shape: no device round trip.  The reference multiplies the Python float T / E by a float32 tensor and takes
+    the ceiling in float32; the same single-precision product is formed here, because a double-precision one
+    lands on the other side of an integer for some shapes (e.g. T = 50290, E = 8, factor 2.4)."""
+    prod = struct.unpack("f", struct.pack("f", num_tokens / num_experts))[0] * \
+        struct.unpack("f", struct.pack("f", capacity_factor))[0]
+    prod = struct.unpack("f", struct.pack("f", prod))[0]      # the product of two floats, rounded to float
+    return max(int(math.ceil(prod)), int(min_capacity))
 
 
 class TopKGatingFunc(torch.autograd.Function):

@@ -66,6 +66,7 @@ class DlblasTritonFusedMoEBlockedF8Impl:
         output = moe_expert_forward(hidden_states, None, None, gate_up_weights, gate_up_scale, down_weights,
                                     down_scale, topk_weights, topk_ids, self.top_k, hidden_states.dtype,
                                     expert_offset, num_experts, _C.QUANT_RECIP_MUL, group_size=self.block_size)
+        _C.maybe_check_status(output.device)
         return output.unflatten(0, input_size[:-1])
 
 
@@ -127,7 +128,9 @@ class FusedMoELowLatency:
             hidden_states, topk_ids, topk_weights, self.num_experts)
         out_states = self.experts(recv_hidden_states, up_weights, up_scale, down_weights, down_scale, masked_m,
                                   expected_m)
-        return self.token_dispatcher.combine(out_states, topk_idx, topk_weights)
+        out = self.token_dispatcher.combine(out_states, topk_idx, topk_weights)
+        _C.maybe_check_status(out.device)
+        return out
 
     def wait(self, event):
         event.current_stream_wait()
@@ -214,6 +217,7 @@ class FusedMoENormal:
             if n == 1:
                 out = self._p2p_experts(self.p2p_chunks[0], hs, topk_ids, topk_weights, up_weights, up_scale,
                                         down_weights, down_scale)
+                _C.maybe_check_status(out.device)
                 return out.view(hidden_states.shape)
             main = torch.cuda.current_stream()
             step = min((t + n - 1) // n, self.p2p_chunks[0].region_rows) if t else 0
@@ -231,6 +235,7 @@ class FusedMoENormal:
                 outs.append(o)
             for st in self._chunk_streams:
                 main.wait_stream(st)
+            _C.maybe_check_status(hs.device)
             return torch.cat(outs, dim=0).view(hidden_states.shape)
         # per_token_group_quant_fp8 fused with the packing of the send buffer (one pass over the tokens)
         x, recv_topk_ids, recv_topk_weights, recv_tokens_per_expert = self.token_dispatcher.dispatch_from_hidden(
@@ -239,7 +244,9 @@ class FusedMoENormal:
         self.token_dispatcher.hidden_shape = hidden_states.shape
         out_states = fused_moe_v3(x, recv_topk_ids, recv_topk_weights, (up_weights, up_scale),
                                   (down_weights, down_scale), recv_tokens_per_expert)
-        return self.token_dispatcher.combine(out_states)
+        out = self.token_dispatcher.combine(out_states)
+        _C.maybe_check_status(out.device)
+        return out
 
     # --- split API used for two-batch overlap (ep_moe.py:100-152) ---
     def capture(self):

@@ -8,6 +8,7 @@ the same point: DeepEP hands back `recv_tokens_per_expert` as a Python list).  R
 unpacked by the permutation / gather kernels of the CUDA extension; the planning below is plain
 torch on small integer tensors and runs on any backend, so it is unit-tested with gloo on CPU.
 """
+import os
 from typing import List, Optional, Tuple, Union
 
 import torch
@@ -430,7 +431,7 @@ class TokenDispatcherP2P:
             return (n + 255) // 256 * 256
 
         sizes = [("q", al(rows * h)), ("s", al(rows * (h // 128) * 4)), ("meta", al(rows * self.meta_ints * 4)),
-                 ("counts", 256), ("comb", al(rows * h * 2))]
+                 ("counts", 256), ("sig", 256), ("comb", al(rows * h * 2))]
         offs, total = {}, 0
         for name, n in sizes:
             offs[name] = total
@@ -452,9 +453,38 @@ class TokenDispatcherP2P:
         self.recv_counts = b[offs["counts"]: offs["counts"] + 256].view(torch.int32)
         self.comb = b[offs["comb"]: offs["comb"] + rows * h * 2].view(params_dtype).view(rows, h)
         self.recv_counts.zero_()
-        self._hdl.barrier(channel=0)
+        # Barriers between the push phases: the extension's own kernel on per-peer signal words (two independent
+        # sets, 64 bytes apart), with a bounded wait that reports through the status word instead of spinning for
+        # ever or trapping.  DLBLAS_EP_BARRIER_TIMEOUT_MS bounds one wait (default 10 s).
+        b[offs["sig"]: offs["sig"] + 256].zero_()
+        self._sig_peers = [(ctypes.c_void_p * w)(*[bb + offs["sig"] + 64 * ch for bb in bases]) for ch in range(2)]
+        self._barrier_no = [0, 0]
+        self.barrier_timeout_ns = int(float(os.environ.get("DLBLAS_EP_BARRIER_TIMEOUT_MS", "10000")) * 1e6)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)          # every rank's words are zero before anyone signals
         self.handle = None
         self.hidden_shape = None
+
+    def barrier(self, channel: int):
+        """Enqueues barrier number n of `channel` on the current stream (n advances by one per call; every rank
+        must make the same calls in the same order).  If a peer does not arrive within the limit, the kernel
+        returns and `_C.check_status()` raises on this rank."""
+        self._barrier_no[channel] += 1
+        dev = self._buf.device
+        _C.check(_C.lib().dlb_p2p_barrier(self._sig_peers[channel], self.world_size, self.rank,
+                                         self._barrier_no[channel] & 0xFFFFFFFF, self.barrier_timeout_ns,
+                                         _C.ptr(_C.status_word(dev)), _C.stream(dev)))
+
+    def resync(self):
+        """After a time-out (a rank skipped or missed a barrier): a host-side collective that brings the barrier
+        numbers of all ranks back in step.  Call it on every rank with no exchange in flight."""
+        dev = self._buf.device
+        torch.cuda.synchronize(dev)
+        n = torch.tensor(self._barrier_no, dtype=torch.int64, device=dev)
+        dist.all_reduce(n, op=dist.ReduceOp.MAX, group=self.group)
+        self._barrier_no = [int(v) for v in n.tolist()]
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=self.group)
 
     def dispatch_from_hidden(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
                              block_size: int = 128):
@@ -462,8 +492,10 @@ class TokenDispatcherP2P:
         expert ids with -1 for unused rows and for slots owned by other ranks."""
         assert block_size == 128
         t, k = topk_idx.shape
+        # checked before anything is pushed or signalled: a rank that raises here has sent nothing; its peers'
+        # next barrier runs into its time limit and reports through the status word
         assert t <= self.region_rows, f"{t} tokens exceed max_tokens_per_rank={self.region_rows}"
-        assert k <= self.kp
+        assert k <= self.kp, f"top_k {k} exceeds the {self.kp} slots the buffers were built for"
         w, dev = self.world_size, hidden_states.device
         self.hidden_shape = hidden_states.shape
         dest = ops.ep_dest_ranks(topk_idx.contiguous(), self.num_local_experts, w)
@@ -476,7 +508,7 @@ class TokenDispatcherP2P:
             _C.ptr(hidden_states), _C.dtype_code(hidden_states.dtype), t, hidden_states.shape[1],
             hidden_states.stride(0), _C.QUANT_DIV_EPS, 1e-10, _C.ptr(within), w, self.rank, self.region_rows,
             p["q"], p["s"], p["meta"], _C.ptr(meta), self.meta_ints, p["counts"], _C.ptr(counts), _C.stream(dev)))
-        self._hdl.barrier(channel=0)
+        self.barrier(0)
         recv_ids = torch.empty(self.rows, k, dtype=torch.int64, device=dev)
         recv_w = torch.empty(self.rows, k, dtype=torch.float32, device=dev)
         _C.check(_C.lib().dlb_p2p_unpack_meta(_C.ptr(self.recv_meta), self.meta_ints, k, _C.ptr(self.recv_counts), w,
@@ -512,7 +544,7 @@ class TokenDispatcherP2P:
 
     def _finish_combine(self, within, t, dtype, dev):
         w = self.world_size
-        self._hdl.barrier(channel=1)
+        self.barrier(1)
         base = (torch.arange(w, device=dev, dtype=torch.int32) * self.region_rows)[None, :]
         idx = torch.where(within >= 0, within + base, torch.full_like(within, -1)).contiguous()
         ones = torch.ones(t, w, dtype=torch.float32, device=dev)

@@ -56,6 +56,14 @@ extern "C" {
 #define DLB_STATUS_TIMEOUT 1
 
 DLB_API int dlb_version(void);
+/* Policy of the bounded barrier waits inside the GEMM kernels, for every launch that follows from any thread
+ * of the process (no counterpart in the reference, whose one device-side wait spins without a limit,
+ * dlblas/kernels/allgather_grpo_loss.py:58-81).  A wait that lasts longer than `limit_cycles` SM clock cycles
+ * makes the kernel stop, give back its tensor memory and set the caller's status word to DLB_STATUS_TIMEOUT;
+ * 0 restores the default of about two seconds.  `withhold_loads` != 0 is a self-test switch: the role that
+ * loads the operands issues nothing, so the first wait of every other role runs out and the time-out path can
+ * be exercised (with a small limit) without any fault on the device; results of such a launch are undefined. */
+DLB_API int dlb_set_wait_policy(uint64_t limit_cycles, int withhold_loads);
 DLB_API const char* dlb_last_error_string(void);
 /* Number of kernels launched by this library on the calling thread since the last reset. */
 DLB_API int64_t dlb_launch_count(int reset);
@@ -225,6 +233,14 @@ DLB_API int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32_t*
  * dlb_p2p_push_rows does.  y [rows * top_k, h] bf16 / fp16, ids int64 [rows, top_k]. */
 DLB_API int dlb_p2p_sum_push(const void* y, int dtype, const int64_t* ids, int top_k, int64_t h, const int32_t* counts,
                      int world, int my_rank, int64_t region_rows, const void* const* peer_dst, void* stream);
+
+/* Barrier among the ranks (one per GPU) between the push phases above; stands in for the ordering DeepEP's
+ * `Buffer.dispatch` / `combine` provide inside the library (dlblas/layers/moe/token_dispatcher.py:345-357, 427-433).
+ * peer_signals[r] points at rank r's array of `world` 32-bit words (zero at start, in memory every rank can
+ * store to); `number` is the barrier's sequence number, 1, 2, 3, ... in the same order on every rank.  The wait
+ * is bounded by `limit_ns`: on expiry *status becomes DLB_STATUS_TIMEOUT and the kernel returns. */
+DLB_API int dlb_p2p_barrier(const void* const* peer_signals, int world, int my_rank, uint32_t number, uint64_t limit_ns,
+                    int32_t* status, void* stream);
 
 /* ---- 16-bit grouped GEMM -----------------------------------------------------------------
  * m_grouped_gemm with trans_b = True (dlblas/kernels/grouped_gemm/BF16/m_grouped_gemm.py:235-352):

@@ -28,6 +28,14 @@ FP8 = torch.float8_e4m3fn
 FP8_MAX = 448.0
 
 
+def _clamp_fp8(v: torch.Tensor) -> torch.Tensor:
+    """`tl.clamp(v, -448, 448)` as the compiled reference kernels evaluate it (dlblas/kernels/moe.py:413,
+    dlblas/kernels/fp8.py:48): min(max(v, -448), 448) with the GPU's non-propagating min / max, which return
+    the non-NaN operand, so NaN (0 / 0 of an all-zero group with scale 0) becomes -448.  torch.clamp and the
+    Triton interpreter propagate NaN instead; the compiled kernel is the one restated here."""
+    return torch.where(torch.isnan(v), torch.full_like(v, -FP8_MAX), v.clamp(-FP8_MAX, FP8_MAX))
+
+
 # --------------------------------------------------------------------------- #
 # quantisation
 # --------------------------------------------------------------------------- #
@@ -35,14 +43,15 @@ def quant_fp8(a: torch.Tensor, group_size: int = 128) -> Tuple[torch.Tensor, tor
     """dlblas/kernels/moe.py:377-421 (`_quant_fp8_kernel`) and :466-474.
 
     scale = absmax * (1/448) (fp32 multiply, no epsilon), q = clamp(a / scale).
-    An all-zero group gives scale 0 and NaN payloads, as in the reference.
+    An all-zero group gives scale 0; its 0 / 0 quotients clamp to -448 (see `_clamp_fp8`), so the
+    payload is finite and the group contributes payload * 0 = 0 to any product.
     """
     assert a.dim() == 2 and a.shape[1] % group_size == 0
     m, k = a.shape
     g = a.to(torch.float32).reshape(m, k // group_size, group_size)
     rmax = torch.tensor(1.0 / FP8_MAX, dtype=torch.float32)
     scale = g.abs().amax(-1) * rmax
-    q = (g / scale[..., None]).clamp(-FP8_MAX, FP8_MAX)
+    q = _clamp_fp8(g / scale[..., None])
     return q.reshape(m, k).to(FP8), scale
 
 
@@ -58,7 +67,7 @@ def per_token_group_quant_fp8(x: torch.Tensor, group_size: int, eps: float = 1e-
     g = x.to(torch.float32).reshape(-1, shp[-1] // group_size, group_size)
     absmax = torch.maximum(g.abs().amax(-1), torch.tensor(eps, dtype=torch.float32))
     scale = absmax / torch.tensor(FP8_MAX, dtype=torch.float32)
-    q = (g / scale[..., None]).clamp(-FP8_MAX, FP8_MAX).reshape(shp).to(FP8)
+    q = _clamp_fp8(g / scale[..., None]).reshape(shp).to(FP8)
     scale = scale.reshape(shp[:-1] + (shp[-1] // group_size,))
     if column_major_scales:
         assert x.dim() == 2
@@ -107,7 +116,7 @@ def silu_and_mul_masked_post_quant(inp: torch.Tensor, masked_m: torch.Tensor, gr
         p = (up * gate).to(torch.float32).reshape(r, n // group_size, group_size)
         absmax = torch.maximum(p.abs().amax(-1), torch.tensor(1e-10, dtype=torch.float32))
         s = absmax / torch.tensor(FP8_MAX, dtype=torch.float32)
-        out[i, :r] = (p / s[..., None]).clamp(-FP8_MAX, FP8_MAX).reshape(r, n)
+        out[i, :r] = _clamp_fp8(p / s[..., None]).reshape(r, n)
         out_s[i, :r] = s
     return out.to(FP8), out_s
 
@@ -271,6 +280,38 @@ def softmax_topk(logits: torch.Tensor, k: int, renormalize: bool = False):
     return w, ids
 
 
+_EXP_TAYLOR = [1.6059043836821613e-10, 2.08767569878681e-09, 2.505210838544172e-08, 2.755731922398589e-07,
+               2.7557319223985893e-06, 2.48015873015873e-05, 0.0001984126984126984, 0.001388888888888889,
+               0.008333333333333333, 0.041666666666666664, 0.16666666666666666, 0.5, 1.0, 1.0]
+
+
+def sigmoid_exact(x: torch.Tensor) -> torch.Tensor:
+    """Canonical sigmoid of the routing scores (`scores = gating_output.sigmoid()`, dlblas/kernels/moe.py:490).
+
+    torch's fp32 sigmoid goes through a library exponential whose last bit differs between CPUs and GPUs, so
+    "the reference's score" is only defined up to one fp32 ulp.  The canonical value used by this oracle and
+    by the CUDA kernel is the fp64 evaluation below, made of individually rounded IEEE multiplies, adds and
+    one divide (every torch call here is one such operation), rounded once to fp32: any IEEE machine
+    reproduces it bit for bit.  It is within one fp32 ulp of torch.sigmoid, so routing decisions differ
+    from a reference run only where two candidates are within an ulp or two of each other."""
+    z = (-x.to(torch.float64)).clamp(-750.0, 750.0)
+    n = torch.round(z * 1.4426950408889634)
+    r = z - n * 0.6931471803691238
+    r = r - n * 1.9082149292705877e-10
+    p = torch.full_like(r, _EXP_TAYLOR[0])
+    for c in _EXP_TAYLOR[1:]:
+        p = p * r + c                       # two roundings: torch does not fuse them
+    ni = n.to(torch.int64)
+    n1 = torch.div(ni, 2, rounding_mode="trunc")
+    n2 = ni - n1
+
+    def pow2(k):
+        return ((k + 1023) << 52).view(torch.float64)
+
+    e = (p * pow2(n1)) * pow2(n2)
+    return (1.0 / (1.0 + e)).to(torch.float32)
+
+
 def biased_grouped_topk(gating_output, correction_bias, topk, renormalize, num_expert_group,
                         topk_group, routed_scaling_factor=None):
     """dlblas/kernels/moe.py:477-521 with canonical tie-breaks: group score = sum of the
@@ -280,7 +321,7 @@ def biased_grouped_topk(gating_output, correction_bias, topk, renormalize, num_e
     chosen experts, divided by their sum when renormalize.  Returns fp32 weights and
     int32 ids.  The reference's `topk(sorted=False)` leaves the slot order open, so ids
     are compared with the reference as per-row sets."""
-    scores = torch.sigmoid(gating_output.to(torch.float32))
+    scores = sigmoid_exact(gating_output.to(torch.float32))
     t, e = scores.shape
     choice = scores + correction_bias.to(torch.float32)[None, :]
     grp = choice.view(t, num_expert_group, -1)
@@ -313,7 +354,8 @@ def topk_gating(logits: torch.Tensor, k: int, capacity_factor: float = 1.0, min_
     lg = logits.to(torch.float32)
     ex = torch.exp(lg)                                   # part1: no max subtraction
     gates = ex / ex.sum(dim=1, keepdim=True)
-    capacity = int(math.ceil((t / e) * (capacity_factor * k)))
+    # float32 product, as `(T / E) * torch.tensor(capacity_factor * k)` evaluates (topk_gating.py:15-24, 254)
+    capacity = int(torch.ceil((t / e) * torch.tensor(capacity_factor * k)).to(torch.int64))
     capacity = max(capacity, int(min_capacity))
     _, ids = _first_max_topk(gates, k)                   # [T, k]
     ids_ks = ids.t().contiguous()                        # [k, T]
