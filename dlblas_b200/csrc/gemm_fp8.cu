@@ -315,14 +315,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const uint64_t a_desc = make_smem_desc(a_addr);
           const uint64_t b_desc = make_smem_desc(a_addr + A_STAGE_BYTES);
           const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-          if (elect_one()) {
-            if constexpr (PAIR) {
+          if constexpr (PAIR) {
+            if (elect_one()) {
 #pragma unroll
               for (int kk = 0; kk < BK / 32; ++kk)
                 tc_mma_f8_pair(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc, kk > 0 ? 1u : 0u);
               tc_commit_pair(empty_bar(s));   // both CTAs' stages
               tc_commit_pair(tfull_bar(b));   // both CTAs' promotion warps
-            } else {
+            }
+          } else {
+            if (elect_one()) {
 #pragma unroll
               for (int kk = 0; kk < BK / 32; ++kk) {
                 // +32 bytes along K inside the 128 B swizzle row == +2 in the (addr >> 4) field
