@@ -17,6 +17,10 @@ the reference path (oracle/) on the host cores on a bounded sample of the same w
 import argparse
 import json
 import os
+
+# torchrun exports OMP_NUM_THREADS=1 to every rank; the CPU baseline leg (rank 0 only) should use the host's cores
+if os.environ.get("LOCAL_RANK") is not None and os.environ.get("OMP_NUM_THREADS") == "1":
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
 import subprocess
 import sys
 import tempfile
