@@ -747,10 +747,13 @@ def run_decode(args):
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize(dev)
-    # On one GPU the layer has no host round trip, so the whole step (about 30 short kernels) replays as one
-    # CUDA graph; with several ranks the all-to-all needs its split sizes on the host and the step runs eagerly.
+    # The layer has no host round trip (one GPU: device-side plan; several ranks: peer-to-peer stores and the
+    # extension's own barrier kernel), so the whole step (about 40 short kernels) replays as one CUDA graph on
+    # every rank.  With DLBLAS_EP_BACKEND=nccl the all-to-all needs its split sizes on the host and the step runs
+    # eagerly.
     run, graphed = step, False
-    if world == 1:
+    host_free = world == 1 or type(layer.token_dispatcher).__name__ == "TokenDispatcherLowLatencyP2P"
+    if host_free:
         try:
             side = torch.cuda.Stream(dev)
             side.wait_stream(torch.cuda.current_stream(dev))
@@ -761,13 +764,19 @@ def run_decode(args):
             with torch.cuda.graph(graph):
                 graph_out = step()                                # noqa: F841  (kept alive with the graph)
             run, graphed = graph.replay, True
-            for _ in range(3):
-                run()
-            torch.cuda.synchronize(dev)
         except Exception as exc:                                  # capture not possible: measure the eager step
             print(f"# CUDA graph capture failed ({type(exc).__name__}: {exc}); timing the eager step", file=sys.stderr)
             run, graphed = step, False
-            torch.cuda.synchronize(dev)
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            # every rank replays, or none does: the barriers inside the step need all ranks in the same mode
+            flag = torch.tensor([1 if graphed else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag[0]) == 0:
+                run, graphed = step, False
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize(dev)
     if world > 1:
         dist.barrier()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
@@ -781,15 +790,31 @@ def run_decode(args):
     if world > 1:
         dist.all_reduce(lat, op=dist.ReduceOp.MAX)            # a step ends when its slowest rank ends
     lat = lat.cpu().sort().values
+    # experts that received at least one row on this rank: their weights (and the shared expert's) are what a step
+    # streams from HBM
+    _, _, _, masked_m, _ = layer.token_dispatcher.dispatch(x, ops.route_softmax_topk(logits, TOPK, True)[1], None, E)
+    if hasattr(layer.token_dispatcher, "barrier"):
+        layer.token_dispatcher.barrier(1)          # the combine's barrier, so that all ranks stay in step
+    e_hit = torch.tensor([float((masked_m > 0).sum())], device=dev)
+    if world > 1:
+        dist.all_reduce(e_hit, op=dist.ReduceOp.MAX)
+    torch.cuda.synchronize(dev)
+    _C.check_status(dev)
     if rank == 0:
         p50 = float(lat[len(lat) // 2])
         p99 = float(lat[min(len(lat) - 1, int(len(lat) * 0.99))])
+        streamed = (float(e_hit[0]) + 1.0) * 3.0 * H * INTER      # e4m3 bytes of w13 + w2 per expert hit, + shared
+        hbm = load_peaks()["hbm_gbs"]
         print(json.dumps({"metric": "moe_decode_layer_latency_ms", "value": p50, "unit": "ms", "p50_ms": p50, "p99_ms": p99,
+                          "experts_hit_max_over_ranks": int(e_hit[0]), "weight_bytes_streamed": streamed,
+                          "hbm_frac_of_measured": streamed / (p50 * 1e-3) / (hbm * 1e9),
                           "tokens_per_s": tokens * world / (p50 * 1e-3), "n_gpus": world, "steps": args.steps,
                           "higher_is_better": False, "dtype": "fp8_e4m3", "data": "synthetic",
                           "config": {"workload": "deepseek_v3_moe_decode", "tokens_per_gpu": tokens, "experts": E,
                                      "top_k": TOPK, "routing": "softmax top-8, Zipf(1.2) expert popularity",
-                                     "parallelism": f"ep{world}", "exchange": "nccl all-to-all, masked layout",
+                                     "parallelism": f"ep{world}",
+                                     "exchange": "peer-to-peer stores, masked layout" if (host_free and world > 1)
+                                     else ("none (one rank)" if world == 1 else "nccl all-to-all, masked layout"),
                                      "cuda_graph": graphed}}))
     if world > 1:
         dist.destroy_process_group()

@@ -56,7 +56,11 @@ SIGNATURES = {
     "dlb_p2p_unpack_meta": (c_int, [c_vp, c_int, c_int, c_vp, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
     "dlb_p2p_sum_push": (c_int, [c_vp, c_int, c_vp, c_int, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
     "dlb_p2p_push_rows": (c_int, [c_vp, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
-    "dlb_p2p_barrier": (c_int, [c_vp, c_int, c_int, ctypes.c_uint32, ctypes.c_uint64, c_vp, c_vp]),
+    "dlb_p2p_barrier": (c_int, [c_vp, c_int, c_int, c_vp, ctypes.c_uint64, c_vp, c_vp]),
+    "dlb_p2p_all_gather_small": (c_int, [c_vp, c_i64, c_int, c_int, c_vp, c_vp]),
+    "dlb_p2p_ll_quant_push": (c_int, [c_vp, c_int, c_i64, c_i64, c_i64, c_int, c_f, c_vp, c_vp, c_int, c_int, c_vp, c_vp,
+                                      c_vp]),
+    "dlb_p2p_push_rows_indexed": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_vp, c_vp]),
     "dlb_grouped_gemm_16bit": (c_int, [c_vp, c_vp, c_int, c_i64, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_vp, c_i64,
                                        c_vp, c_vp]),
     "dlb_moe_build_tiles_rows": (c_int, [c_vp, c_vp, c_int, c_int, c_int, c_vp, c_int, c_vp]),

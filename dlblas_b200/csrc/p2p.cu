@@ -179,13 +179,22 @@ __global__ void __launch_bounds__(THREADS) sum_push_kernel(const T* __restrict__
 // word per peer; arriving means storing the barrier's number (a counter that every rank advances in step) into
 // word "my rank" of every peer's array with release semantics at system scope, so that everything this rank
 // stored into the peers' memory before, from earlier kernels of the stream included, is visible to a peer that
-// has seen the number.  Then thread r waits until word r of the own array has reached the number.  The wait is
+// has seen the number.  Then thread r waits until word r of the own array has reached the number.  The number is
+// this rank's count of barriers on these words (kept in device memory and advanced by the kernel).  The wait is
 // bounded: when `limit_ns` nanoseconds have passed the kernel records DLB_STATUS_TIMEOUT in the status word and
 // returns; it never traps and never spins without a limit, so a rank that died or raised before its arrival
 // costs its peers one time-out and an exception on the host, not a hung GPU.  Plain peer stores and loads only.
-__global__ void __launch_bounds__(32) rank_barrier_kernel(PeerPtrs signals, int world, int my_rank, uint32_t number,
-                                                          unsigned long long limit_ns, int* __restrict__ status) {
+__global__ void __launch_bounds__(32) rank_barrier_kernel(PeerPtrs signals, int world, int my_rank,
+                                                          uint32_t* __restrict__ counter, unsigned long long limit_ns,
+                                                          int* __restrict__ status) {
   const int r = threadIdx.x;
+  // the barrier's number lives on the device, so that a launch replayed from a CUDA graph still counts on
+  uint32_t number = 0;
+  if (r == 0) {
+    number = *counter + 1u;
+    *counter = number;
+  }
+  number = __shfl_sync(0xffffffffu, number, 0);
   if (r >= world) return;
   __threadfence_system();
   uint32_t* theirs = reinterpret_cast<uint32_t*>(signals.p[r]) + my_rank;
@@ -201,6 +210,79 @@ __global__ void __launch_bounds__(32) rank_barrier_kernel(PeerPtrs signals, int 
       break;
     }
     __nanosleep(200);
+  }
+}
+
+// ---- low-latency (masked layout) exchange ---------------------------------------------------------------------
+// Copies this rank's small vector (`vecs` 16-byte words) into slot "my rank" of the same array on every peer: an
+// all-gather by stores.
+__global__ void __launch_bounds__(THREADS) all_gather_small_kernel(const uint4* __restrict__ src, int vecs, int world,
+                                                                   int my_rank, PeerPtrs dst) {
+  const int d = blockIdx.y;
+  if (d >= world) return;
+  uint4* out = reinterpret_cast<uint4*>(dst.p[d]) + (long long)my_rank * vecs;
+  for (int i = blockIdx.x * THREADS + threadIdx.x; i < vecs; i += gridDim.x * THREADS) out[i] = __ldg(src + i);
+}
+
+// Quantises every token once and stores its row and scales for each of its routed slots straight into the masked
+// layout of the rank that owns the slot's expert: slot f goes to rank pair_rank[f] (< 0: nowhere), row pair_row[f]
+// of that rank's [E_local * rows_per_expert, k] buffer.
+template <bool IS_BF16>
+__global__ void __launch_bounds__(THREADS) ll_quant_push_kernel(const void* __restrict__ x, long long tokens, long long k,
+                                                                long long ldx, int mode, float eps,
+                                                                const int* __restrict__ pair_rank,
+                                                                const int* __restrict__ pair_row, int top_k,
+                                                                PeerPtrs peer_q, PeerPtrs peer_s) {
+  const long long vec_per_row = k / 8;
+  const long long total = tokens * vec_per_row;
+  const long long groups = k / 128;
+  for (long long u0 = (long long)blockIdx.x * THREADS; u0 < total; u0 += (long long)gridDim.x * THREADS) {
+    const long long u = u0 + threadIdx.x;
+    const bool active = u < total;
+    const long long row = active ? u / vec_per_row : 0;
+    const long long c = active ? (u - row * vec_per_row) * 8 : 0;
+    float v[8];
+    if (active) {
+      if (IS_BF16) load8_bf16(reinterpret_cast<const __nv_bfloat16*>(x) + row * ldx + c, v);
+      else load8_f16(reinterpret_cast<const __half*>(x) + row * ldx + c, v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = mode == DLB_QUANT_RECIP_MUL ? amax * (1.0f / 448.0f) : fmaxf(amax, eps) / 448.0f;
+    if (!active) continue;
+    uint2 packed;
+    packed.x = (uint32_t)f32x2_to_e4m3x2(v[0] / scale, v[1] / scale) |
+               ((uint32_t)f32x2_to_e4m3x2(v[2] / scale, v[3] / scale) << 16);
+    packed.y = (uint32_t)f32x2_to_e4m3x2(v[4] / scale, v[5] / scale) |
+               ((uint32_t)f32x2_to_e4m3x2(v[6] / scale, v[7] / scale) << 16);
+    const bool first = ((c / 8) & 15) == 0;
+    for (int j = 0; j < top_k; ++j) {
+      const int r = __ldg(pair_rank + row * top_k + j);
+      if (r < 0) continue;
+      const long long drow = __ldg(pair_row + row * top_k + j);
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(peer_q.p[r]) + drow * k + c) = packed;
+      if (first) reinterpret_cast<float*>(peer_s.p[r])[drow * groups + c / 128] = scale;
+    }
+  }
+}
+
+// Row i of `src` goes to rank row_rank[i] (< 0: nowhere), row row_pos[i] of that rank's buffer.
+__global__ void __launch_bounds__(THREADS) push_rows_indexed_kernel(const uint4* __restrict__ src, long long vec_per_row,
+                                                                    long long rows, const int* __restrict__ row_rank,
+                                                                    const int* __restrict__ row_pos, PeerPtrs peer_dst) {
+  const long long total = rows * vec_per_row;
+  for (long long u = (long long)blockIdx.x * THREADS + threadIdx.x; u < total; u += (long long)gridDim.x * THREADS) {
+    const long long row = u / vec_per_row;
+    const int r = __ldg(row_rank + row);
+    if (r < 0) continue;
+    const long long c = u - row * vec_per_row;
+    reinterpret_cast<uint4*>(peer_dst.p[r])[(long long)__ldg(row_pos + row) * vec_per_row + c] = __ldg(src + u);
   }
 }
 
@@ -324,19 +406,85 @@ extern "C" int dlb_p2p_sum_push(const void* y, int dtype, const int64_t* ids, in
   return DLB_OK;
 }
 
-extern "C" int dlb_p2p_barrier(const void* const* peer_signals, int world, int my_rank, uint32_t number,
+extern "C" int dlb_p2p_barrier(const void* const* peer_signals, int world, int my_rank, uint32_t* counter,
                                uint64_t limit_ns, int32_t* status, void* stream) {
   DLB_REQUIRE(world > 0 && world <= MAX_WORLD && my_rank >= 0 && my_rank < world, DLB_ERR_INVALID,
               "p2p_barrier: world=%d (max %d), rank=%d", world, MAX_WORLD, my_rank);
   DLB_REQUIRE(limit_ns > 0, DLB_ERR_INVALID, "p2p_barrier: the wait needs a limit");
+  DLB_REQUIRE(counter != nullptr, DLB_ERR_INVALID, "p2p_barrier: null counter");
   PeerPtrs ps;
   for (int r = 0; r < world; ++r) {
     DLB_REQUIRE(peer_signals != nullptr && peer_signals[r] != nullptr && (uintptr_t)peer_signals[r] % 4 == 0,
                 DLB_ERR_INVALID, "p2p_barrier: bad signal pointer for rank %d", r);
     ps.p[r] = const_cast<void*>(peer_signals[r]);
   }
-  rank_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ps, world, my_rank, number, limit_ns, status);
+  rank_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ps, world, my_rank, counter, limit_ns, status);
   count_launch();
   DLB_CHECK_LAUNCH("rank_barrier_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_p2p_all_gather_small(const void* src, int64_t bytes, int world, int my_rank,
+                                        const void* const* peer_dst, void* stream) {
+  DLB_REQUIRE(src && bytes > 0 && bytes % 16 == 0 && (uintptr_t)src % 16 == 0 && bytes <= (1 << 24), DLB_ERR_INVALID,
+              "p2p_all_gather_small: bytes=%lld must be a positive multiple of 16 (at most 16 MiB), src 16-byte aligned",
+              (long long)bytes);
+  DLB_REQUIRE(world > 0 && world <= MAX_WORLD && my_rank >= 0 && my_rank < world, DLB_ERR_INVALID,
+              "p2p_all_gather_small: world=%d (max %d), rank=%d", world, MAX_WORLD, my_rank);
+  PeerPtrs pd;
+  int rc = fill_peers(pd, peer_dst, world, "p2p_all_gather_small");
+  if (rc != DLB_OK) return rc;
+  const int vecs = (int)(bytes / 16);
+  dim3 grid((unsigned)min((long long)ceil_div(vecs, THREADS), 64ll), (unsigned)world);
+  all_gather_small_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint4*>(src), vecs, world,
+                                                                     my_rank, pd);
+  count_launch();
+  DLB_CHECK_LAUNCH("all_gather_small_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_p2p_ll_quant_push(const void* x, int x_dtype, int64_t tokens, int64_t k, int64_t ldx, int mode,
+                                     float eps, const int32_t* pair_rank, const int32_t* pair_row, int top_k, int world,
+                                     const void* const* peer_q, const void* const* peer_scales, void* stream) {
+  DLB_REQUIRE(tokens >= 0 && k > 0 && k % 128 == 0, DLB_ERR_INVALID, "p2p_ll_quant_push: k=%lld must be a multiple of 128",
+              (long long)k);
+  DLB_REQUIRE(world > 0 && world <= MAX_WORLD && top_k > 0, DLB_ERR_INVALID, "p2p_ll_quant_push: bad world / top_k");
+  DLB_REQUIRE(x_dtype == DLB_BF16 || x_dtype == DLB_F16, DLB_ERR_INVALID, "p2p_ll_quant_push: x must be bf16 or fp16");
+  DLB_REQUIRE(mode == DLB_QUANT_RECIP_MUL || mode == DLB_QUANT_DIV_EPS, DLB_ERR_INVALID, "p2p_ll_quant_push: bad mode");
+  if (tokens == 0) return DLB_OK;
+  DLB_REQUIRE(x && pair_rank && pair_row, DLB_ERR_INVALID, "p2p_ll_quant_push: null pointer");
+  DLB_REQUIRE((uintptr_t)x % 16 == 0 && (ldx * 2) % 16 == 0, DLB_ERR_INVALID,
+              "p2p_ll_quant_push: x rows must be 16-byte aligned");
+  PeerPtrs pq, ps;
+  int rc;
+  if ((rc = fill_peers(pq, peer_q, world, "p2p_ll_quant_push(q)")) != DLB_OK) return rc;
+  if ((rc = fill_peers(ps, peer_scales, world, "p2p_ll_quant_push(scales)")) != DLB_OK) return rc;
+  const int grid = grid_for(tokens * (k / 8));
+  cudaStream_t st = (cudaStream_t)stream;
+  if (x_dtype == DLB_BF16)
+    ll_quant_push_kernel<true><<<grid, THREADS, 0, st>>>(x, tokens, k, ldx, mode, eps, pair_rank, pair_row, top_k, pq, ps);
+  else
+    ll_quant_push_kernel<false><<<grid, THREADS, 0, st>>>(x, tokens, k, ldx, mode, eps, pair_rank, pair_row, top_k, pq, ps);
+  count_launch();
+  DLB_CHECK_LAUNCH("ll_quant_push_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_p2p_push_rows_indexed(const void* src, int64_t row_bytes, int64_t rows, const int32_t* row_rank,
+                                         const int32_t* row_pos, int world, const void* const* peer_dst, void* stream) {
+  DLB_REQUIRE(rows >= 0 && row_bytes > 0 && row_bytes % 16 == 0, DLB_ERR_INVALID,
+              "p2p_push_rows_indexed: rows must be multiples of 16 bytes");
+  DLB_REQUIRE(world > 0 && world <= MAX_WORLD, DLB_ERR_INVALID, "p2p_push_rows_indexed: bad world");
+  if (rows == 0) return DLB_OK;
+  DLB_REQUIRE(src && row_rank && row_pos && (uintptr_t)src % 16 == 0, DLB_ERR_INVALID,
+              "p2p_push_rows_indexed: null or misaligned pointer");
+  PeerPtrs pd;
+  int rc = fill_peers(pd, peer_dst, world, "p2p_push_rows_indexed");
+  if (rc != DLB_OK) return rc;
+  const long long vpr = row_bytes / 16;
+  push_rows_indexed_kernel<<<grid_for(rows * vpr), THREADS, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const uint4*>(src), vpr, rows, row_rank, row_pos, pd);
+  count_launch();
+  DLB_CHECK_LAUNCH("push_rows_indexed_kernel");
   return DLB_OK;
 }

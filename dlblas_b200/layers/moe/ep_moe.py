@@ -17,7 +17,8 @@ from ...utils.logger import get_logger
 from ...utils.utils import DisposibleTensor
 from .experts_distribution_recorder import ExpertsDistributionRecorder
 from .kernels.blocked_fp8_fused_moe import _renormalize, moe_expert_forward
-from .token_dispatcher import TokenDispatcherLowLatency, TokenDispatcherNormal, TokenDispatcherP2P
+from .token_dispatcher import (TokenDispatcherLowLatency, TokenDispatcherLowLatencyP2P, TokenDispatcherNormal,
+                               TokenDispatcherP2P)
 
 logger = get_logger(__name__)
 
@@ -82,9 +83,13 @@ class FusedMoELowLatency:
         self.layer_index = layer_index
         self.block_size = block_size
         self.out_dtype = out_dtype
-        self.token_dispatcher = TokenDispatcherLowLatency(group=ep_group, num_experts=num_experts,
-                                                          num_local_experts=num_experts // ep_size,
-                                                          hidden_size=hidden_dim, params_dtype=out_dtype)
+        # Exchange backend: with more than one rank the default is the peer-to-peer dispatcher (in-kernel stores
+        # into the owners' masked layouts, no host round trip, CUDA-graph capturable); DLBLAS_EP_BACKEND=nccl
+        # selects the all-to-all with host-side split sizes.
+        backend = os.environ.get("DLBLAS_EP_BACKEND", "p2p" if ep_size > 1 else "nccl").lower()
+        cls = TokenDispatcherLowLatencyP2P if (backend == "p2p" and ep_size > 1) else TokenDispatcherLowLatency
+        self.token_dispatcher = cls(group=ep_group, num_experts=num_experts, num_local_experts=num_experts // ep_size,
+                                    hidden_size=hidden_dim, params_dtype=out_dtype)
 
     def experts(self, hidden_states_fp8, gate_up_weight: torch.Tensor, gate_up_scale: torch.Tensor,
                 gate_down_weight: torch.Tensor, gate_down_scale: torch.Tensor, masked_m: torch.Tensor,

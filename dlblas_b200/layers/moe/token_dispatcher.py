@@ -393,8 +393,229 @@ class TokenDispatcherLowLatency:
 
 
 # ----------------------------------------------------------------------------------------------
+# low-latency (decode) mode over peer-to-peer stores: no host synchronisation at any number of ranks
+# ----------------------------------------------------------------------------------------------
+def make_low_latency_p2p_plan(c: torch.Tensor, me: int, num_local_experts: int, rows_per_expert: int,
+                              topk_idx: torch.Tensor, rank_in: torch.Tensor):
+    """Index arithmetic of the host-free low-latency exchange (plain torch on small integer tensors, any device).
+
+    c int64 [W, E]: pair count of every source rank for every global expert (the all-gathered counts);
+    topk_idx int64 [T, k] (negative: no expert); rank_in int32 [T * k]: rank of a pair among this rank's pairs of
+    the same expert.  The rows of an expert's block on its owner are ordered by source rank, and inside a source by
+    that rank; a rank's send order is by expert, then by that rank.  Returns, for this rank as a SOURCE,
+    pair_rank / pair_row int32 [T * k] (owner rank and row of its [E_local * rows_per_expert] buffer, -1 = not
+    sent: no expert, or the expert's block is full), pair_pos int32 [T * k] (row of this rank's own return buffer)
+    and the mask `sent`; and, for this rank as an OWNER, masked_m int32 [E_local] and row_rank / row_pos int32
+    [E_local * rows_per_expert]: source rank and return-buffer row of every row of its masked layout (-1 = unused)."""
+    w, e = c.shape
+    nle, rpe = num_local_experts, rows_per_expert
+    dev = c.device
+    ids = topk_idx.reshape(-1)
+    valid = ids >= 0
+    e_safe = ids.clamp(min=0)
+    rows_before_me = c[:me].sum(dim=0)                           # rows of earlier sources, per expert
+    row_in_expert = rows_before_me[e_safe] + rank_in.to(torch.int64)
+    sent = valid & (row_in_expert < rpe)                         # an overfull expert drops its last arrivals
+    neg = torch.full_like(ids, -1)
+    pair_rank = torch.where(sent, e_safe // nle, neg).to(torch.int32)
+    pair_row = torch.where(sent, (e_safe % nle) * rpe + row_in_expert, neg).to(torch.int32)
+    sent_before = torch.cumsum(c[me], 0) - c[me]                 # this rank's pairs of lower experts
+    pair_pos = torch.where(sent, sent_before[e_safe] + rank_in.to(torch.int64), neg).to(torch.int32)
+    lo = me * nle
+    loc = c[:, lo:lo + nle]                                      # [W, E_local]
+    ends = torch.cumsum(loc, dim=0)                              # rows of sources 0..r, per local expert
+    masked_m = ends[-1].clamp(max=rpe).to(torch.int32)
+    row = torch.arange(rpe, device=dev, dtype=torch.int64)
+    src = torch.searchsorted(ends.t().contiguous(), row[None, :].expand(nle, rpe).contiguous(), right=True)
+    live = src < w
+    src_c = src.clamp(max=w - 1)
+    le_idx = torch.arange(nle, device=dev)[:, None].expand(nle, rpe)
+    first_row = (ends - loc)[src_c, le_idx]                      # first row of that source inside the expert
+    pairs_before = (torch.cumsum(c, dim=1) - c)[:, lo:lo + nle]  # [W, E_local]: the source's pairs of lower experts
+    src_pos = pairs_before[src_c, le_idx] + (row[None, :] - first_row)
+    row_rank = torch.where(live, src_c, torch.full_like(src_c, -1)).to(torch.int32).reshape(-1)
+    row_pos = torch.where(live, src_pos, torch.full_like(src_pos, -1)).to(torch.int32).reshape(-1)
+    return pair_rank, pair_row, pair_pos, sent, masked_m, row_rank, row_pos
+
+
+class TokenDispatcherLowLatencyP2P:
+    """`DeepEPTokenDispatcherLowLatency` of the reference (token_dispatcher.py:455-602) on symmetric memory.
+
+    dispatch: the (token, slot) pairs are ranked inside their expert by the sort kernel; every rank stores its
+    per-expert pair counts into all peers (an all-gather by stores) and, after a barrier, knows where its rows
+    start inside every expert's block on the owning rank (rows of source 0 first, then source 1, ...).  One kernel
+    then quantises each token once and stores it for each routed slot straight into the masked layout
+    [E_local, max_tokens_per_rank * world, H] of the owner.  combine: the experts' rows go back to the rank they
+    came from by indexed stores, and a weighted gather sums a token's slots.  Split sizes never reach the host,
+    so the step can be captured in a CUDA graph on every rank.  All ranks must construct the dispatcher
+    collectively and call dispatch / combine in the same order."""
+
+    def __init__(self, group, num_experts: int = None, num_local_experts: int = None, hidden_size: int = None,
+                 params_dtype: torch.dtype = None, return_recv_hook: bool = False,
+                 num_max_dispatch_tokens_per_rank: int = 128, max_top_k: int = 8):
+        self.group = group
+        self.num_experts = num_experts
+        self.num_local_experts = num_local_experts
+        self.hidden_size = hidden_size
+        self.params_dtype = params_dtype or torch.bfloat16
+        self.world_size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        assert num_experts == num_local_experts * self.world_size, "experts must split evenly over the ranks"
+        assert hidden_size % 128 == 0 and self.params_dtype in (torch.bfloat16, torch.float16)
+        self.num_max_dispatch_tokens_per_rank = int(os.getenv("DEEPEP_MAX_TOKENS_PER_RANK",
+                                                              str(num_max_dispatch_tokens_per_rank)))
+        self.max_top_k = int(max_top_k)
+        self.return_recv_hook = return_recv_hook
+        w, h, nle, rpe = self.world_size, hidden_size, num_local_experts, self.rows_per_expert
+        self.cnt_ints = (num_experts + 3) // 4 * 4                 # counts travel as whole 16-byte words
+        self.send_rows = self.num_max_dispatch_tokens_per_rank * self.max_top_k
+        sizes = [("allcnt", w * self.cnt_ints * 4), ("q", nle * rpe * h), ("s", nle * rpe * (h // 128) * 4),
+                 ("comb", self.send_rows * h * 2)]
+        self._sym = _SymmetricBuffers(group, sizes)
+        self.allcnt = self._sym.region("allcnt", w * self.cnt_ints * 4).view(torch.int32).view(w, self.cnt_ints)
+        self.recv_q = self._sym.region("q", nle * rpe * h).view(ops.FP8).view(nle, rpe, h)
+        self.recv_s = self._sym.region("s", nle * rpe * (h // 128) * 4).view(torch.float32).view(nle, rpe, h // 128)
+        self.comb = self._sym.region("comb", self.send_rows * h * 2).view(self.params_dtype).view(self.send_rows, h)
+        self.allcnt.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        self.handle = None
+
+    @property
+    def rows_per_expert(self):
+        return self.num_max_dispatch_tokens_per_rank * self.world_size
+
+    def barrier(self, channel: int):
+        self._sym.barrier(channel)
+
+    def resync(self):
+        self._sym.resync()
+
+    def dispatch(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+                 num_experts: int, use_fp8: bool = True):
+        if num_experts is not None and self.num_experts is not None:
+            assert self.num_experts == num_experts
+        topk_idx = topk_idx.to(torch.int64)
+        expected_m = (hidden_states.shape[0] * self.world_size * topk_idx.shape[1] + num_experts) // num_experts
+        packed, masked_m, self.handle, event, _ = self.dispatch_async(hidden_states, topk_idx, num_experts, use_fp8,
+                                                                      async_finish=False)
+        return packed, topk_idx, topk_weights, masked_m, expected_m
+
+    def dispatch_async(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, num_experts: Optional[int] = None,
+                       use_fp8: bool = True, async_finish: bool = True):
+        assert topk_idx.dtype == torch.int64
+        assert use_fp8, "the masked layout of this package is FP8"
+        t, k = topk_idx.shape
+        # limits are checked before anything is stored or signalled (a rank that raises here has sent nothing)
+        assert t <= self.num_max_dispatch_tokens_per_rank, "more tokens than num_max_dispatch_tokens_per_rank"
+        assert k <= self.max_top_k, "more slots per token than the buffers were built for"
+        e, nle, w, me, rpe = self.num_experts, self.num_local_experts, self.world_size, self.rank, self.rows_per_expert
+        dev = hidden_states.device
+        sym = self._sym
+        # rank of every pair inside its expert (among this rank's pairs) and this rank's pair count per expert
+        _, _, _, rank_in, counts = ops.sort_by_expert(topk_idx, e, want_rank=True, want_counts=True)
+        if self.cnt_ints != e:
+            counts = torch.cat([counts, counts.new_zeros(self.cnt_ints - e)])
+        _C.check(_C.lib().dlb_p2p_all_gather_small(_C.ptr(counts), self.cnt_ints * 4, w, me, sym.peers["allcnt"],
+                                                  _C.stream(dev)))
+        sym.barrier(0)
+        c = self.allcnt[:, :e].to(torch.int64)                       # [W(source), E]: a private copy of the counts
+        pair_rank, pair_row, pair_pos, sent, masked_m, row_rank, row_pos = make_low_latency_p2p_plan(
+            c, me, nle, rpe, topk_idx, rank_in)
+        _C.check(_C.lib().dlb_p2p_ll_quant_push(
+            _C.ptr(hidden_states), _C.dtype_code(hidden_states.dtype), t, hidden_states.shape[1],
+            hidden_states.stride(0), _C.QUANT_DIV_EPS, 1e-10, _C.ptr(pair_rank), _C.ptr(pair_row), k, w,
+            sym.peers["q"], sym.peers["s"], _C.stream(dev)))
+        sym.barrier(0)
+        plan = (pair_pos.view(t, k), sent.view(t, k), row_rank, row_pos, t)
+        return [self.recv_q, self.recv_s], masked_m, plan, _record_event(), (lambda: None)
+
+    def combine(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor):
+        out, _, _ = self.combine_async(hidden_states, topk_idx.to(torch.int64), topk_weights.to(torch.float32),
+                                       self.handle, async_finish=False)
+        return out
+
+    def combine_async(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+                      handle: Tuple, async_finish: bool):
+        assert topk_idx.dtype == torch.int64
+        assert topk_weights.dtype == torch.float32
+        pair_pos, sent, row_rank, row_pos, t = handle
+        nle, rpe, h = hidden_states.shape
+        assert hidden_states.dtype == self.comb.dtype and hidden_states.is_contiguous()
+        dev = hidden_states.device
+        sym = self._sym
+        _C.check(_C.lib().dlb_p2p_push_rows_indexed(_C.ptr(hidden_states), h * hidden_states.element_size(), nle * rpe,
+                                                   _C.ptr(row_rank), _C.ptr(row_pos), self.world_size,
+                                                   sym.peers["comb"], _C.stream(dev)))
+        sym.barrier(1)
+        out = torch.empty(t, h, dtype=hidden_states.dtype, device=dev)
+        ids32 = torch.where(sent, topk_idx, torch.full_like(topk_idx, -1)).to(torch.int32).contiguous()
+        # out[t] = sum_k w[t, k] * comb[pair_pos[t, k]]
+        ops.ep_gather(self.comb, ids32, topk_weights.contiguous(), pair_pos.contiguous(), out)
+        return out, _record_event(), (lambda: None)
+
+
+# ----------------------------------------------------------------------------------------------
 # normal (prefill) mode over peer-to-peer stores: no host synchronisation, no staging copies
 # ----------------------------------------------------------------------------------------------
+class _SymmetricBuffers:
+    """One symmetric-memory allocation per rank cut into named regions, the peers' addresses of every region, and
+    the extension's bounded barrier on per-peer signal words (two independent sets, "channels")."""
+
+    def __init__(self, group, regions):
+        """regions: list of (name, bytes); all ranks must construct this collectively with equal sizes."""
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.world_size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        w = self.world_size
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.device = dev
+
+        def al(n):
+            return (n + 255) // 256 * 256
+
+        offs, total = {}, 0
+        for name, n in list(regions) + [("sig", 256)]:
+            offs[name] = total
+            total += al(n)
+        gname = group.group_name if hasattr(group, "group_name") else group
+        self._buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        self._hdl = symm_mem.rendezvous(self._buf, gname)
+        bases = [int(p) for p in self._hdl.buffer_ptrs]
+        self.offs = offs
+        self.peers = {name: (ctypes.c_void_p * w)(*[b + offs[name] for b in bases]) for name in offs}
+        self._buf[offs["sig"]: offs["sig"] + 256].zero_()
+        self._sig_peers = [(ctypes.c_void_p * w)(*[bb + offs["sig"] + 64 * ch for bb in bases]) for ch in range(2)]
+        # this rank's count of barriers per channel, on the device (the barrier kernel advances it)
+        self._barrier_no = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.barrier_timeout_ns = int(float(os.environ.get("DLBLAS_EP_BARRIER_TIMEOUT_MS", "10000")) * 1e6)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)          # every rank's words are zero before anyone signals
+
+    def region(self, name, nbytes):
+        o = self.offs[name]
+        return self._buf[o: o + nbytes]
+
+    def barrier(self, channel: int):
+        """Enqueues the next barrier of `channel` on the current stream (every rank must make the same calls in
+        the same order).  If a peer does not arrive within DLBLAS_EP_BARRIER_TIMEOUT_MS (default 10 s), the kernel
+        returns and `_C.check_status()` raises on this rank."""
+        _C.check(_C.lib().dlb_p2p_barrier(self._sig_peers[channel], self.world_size, self.rank,
+                                         _C.ptr(self._barrier_no[channel]), self.barrier_timeout_ns,
+                                         _C.ptr(_C.status_word(self.device)), _C.stream(self.device)))
+
+    def resync(self):
+        """After a time-out (a rank skipped or missed a barrier): a host-side collective that brings the barrier
+        counts of all ranks back in step.  Call it on every rank with no exchange in flight."""
+        torch.cuda.synchronize(self.device)
+        dist.all_reduce(self._barrier_no, op=dist.ReduceOp.MAX, group=self.group)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
+
 class TokenDispatcherP2P:
     """Dispatch / combine through symmetric memory (`torch.distributed._symmetric_memory`): the
     quantiser of the extension stores every token's FP8 row, scales and routing metadata directly
@@ -407,9 +628,6 @@ class TokenDispatcherP2P:
 
     def __init__(self, group, num_experts: int, num_local_experts: int, hidden_size: int,
                  params_dtype: torch.dtype = torch.bfloat16, max_tokens_per_rank: int = 8192, max_top_k: int = 8):
-        import ctypes
-
-        import torch.distributed._symmetric_memory as symm_mem
         self.group = group
         self.num_experts = num_experts
         self.num_local_experts = num_local_experts
@@ -425,66 +643,28 @@ class TokenDispatcherP2P:
         w, h = self.world_size, hidden_size
         rows = w * self.region_rows
         self.rows = rows
-        dev = torch.device("cuda", torch.cuda.current_device())
-
-        def al(n):
-            return (n + 255) // 256 * 256
-
-        sizes = [("q", al(rows * h)), ("s", al(rows * (h // 128) * 4)), ("meta", al(rows * self.meta_ints * 4)),
-                 ("counts", 256), ("sig", 256), ("comb", al(rows * h * 2))]
-        offs, total = {}, 0
-        for name, n in sizes:
-            offs[name] = total
-            total += n
-        gname = group.group_name if hasattr(group, "group_name") else group
-        try:
-            if not symm_mem.is_symm_mem_enabled_for_group(gname):
-                symm_mem.enable_symm_mem_for_group(gname)
-        except Exception:      # newer torch enables groups on first rendezvous
-            pass
-        self._buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
-        self._hdl = symm_mem.rendezvous(self._buf, gname)
-        bases = [int(p) for p in self._hdl.buffer_ptrs]
-        self._peers = {name: (ctypes.c_void_p * w)(*[b + offs[name] for b in bases]) for name, _ in sizes}
-        b = self._buf
-        self.recv_q = b[offs["q"]: offs["q"] + rows * h].view(ops.FP8).view(rows, h)
-        self.recv_s = b[offs["s"]: offs["s"] + rows * (h // 128) * 4].view(torch.float32).view(rows, h // 128)
-        self.recv_meta = b[offs["meta"]: offs["meta"] + rows * self.meta_ints * 4].view(torch.int32).view(rows, -1)
-        self.recv_counts = b[offs["counts"]: offs["counts"] + 256].view(torch.int32)
-        self.comb = b[offs["comb"]: offs["comb"] + rows * h * 2].view(params_dtype).view(rows, h)
+        sizes = [("q", rows * h), ("s", rows * (h // 128) * 4), ("meta", rows * self.meta_ints * 4), ("counts", 256),
+                 ("comb", rows * h * 2)]
+        self._sym = _SymmetricBuffers(group, sizes)
+        self._peers = self._sym.peers
+        self.recv_q = self._sym.region("q", rows * h).view(ops.FP8).view(rows, h)
+        self.recv_s = self._sym.region("s", rows * (h // 128) * 4).view(torch.float32).view(rows, h // 128)
+        self.recv_meta = self._sym.region("meta", rows * self.meta_ints * 4).view(torch.int32).view(rows, -1)
+        self.recv_counts = self._sym.region("counts", 256).view(torch.int32)
+        self.comb = self._sym.region("comb", rows * h * 2).view(params_dtype).view(rows, h)
         self.recv_counts.zero_()
-        # Barriers between the push phases: the extension's own kernel on per-peer signal words (two independent
-        # sets, 64 bytes apart), with a bounded wait that reports through the status word instead of spinning for
-        # ever or trapping.  DLBLAS_EP_BARRIER_TIMEOUT_MS bounds one wait (default 10 s).
-        b[offs["sig"]: offs["sig"] + 256].zero_()
-        self._sig_peers = [(ctypes.c_void_p * w)(*[bb + offs["sig"] + 64 * ch for bb in bases]) for ch in range(2)]
-        self._barrier_no = [0, 0]
-        self.barrier_timeout_ns = int(float(os.environ.get("DLBLAS_EP_BARRIER_TIMEOUT_MS", "10000")) * 1e6)
-        torch.cuda.synchronize(dev)
-        dist.barrier(group=group)          # every rank's words are zero before anyone signals
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
         self.handle = None
         self.hidden_shape = None
 
     def barrier(self, channel: int):
-        """Enqueues barrier number n of `channel` on the current stream (n advances by one per call; every rank
-        must make the same calls in the same order).  If a peer does not arrive within the limit, the kernel
-        returns and `_C.check_status()` raises on this rank."""
-        self._barrier_no[channel] += 1
-        dev = self._buf.device
-        _C.check(_C.lib().dlb_p2p_barrier(self._sig_peers[channel], self.world_size, self.rank,
-                                         self._barrier_no[channel] & 0xFFFFFFFF, self.barrier_timeout_ns,
-                                         _C.ptr(_C.status_word(dev)), _C.stream(dev)))
+        """Enqueues the next barrier of `channel` on the current stream; see `_SymmetricBuffers.barrier`."""
+        self._sym.barrier(channel)
 
     def resync(self):
-        """After a time-out (a rank skipped or missed a barrier): a host-side collective that brings the barrier
-        numbers of all ranks back in step.  Call it on every rank with no exchange in flight."""
-        dev = self._buf.device
-        torch.cuda.synchronize(dev)
-        n = torch.tensor(self._barrier_no, dtype=torch.int64, device=dev)
-        dist.all_reduce(n, op=dist.ReduceOp.MAX, group=self.group)
-        self._barrier_no = [int(v) for v in n.tolist()]
-        torch.cuda.synchronize(dev)
-        dist.barrier(group=self.group)
+        """Brings the barrier counts of all ranks back in step after a time-out; see `_SymmetricBuffers.resync`."""
+        self._sym.resync()
 
     def dispatch_from_hidden(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
                              block_size: int = 128):

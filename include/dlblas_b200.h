@@ -237,10 +237,27 @@ DLB_API int dlb_p2p_sum_push(const void* y, int dtype, const int64_t* ids, int t
 /* Barrier among the ranks (one per GPU) between the push phases above; stands in for the ordering DeepEP's
  * `Buffer.dispatch` / `combine` provide inside the library (dlblas/layers/moe/token_dispatcher.py:345-357, 427-433).
  * peer_signals[r] points at rank r's array of `world` 32-bit words (zero at start, in memory every rank can
- * store to); `number` is the barrier's sequence number, 1, 2, 3, ... in the same order on every rank.  The wait
- * is bounded by `limit_ns`: on expiry *status becomes DLB_STATUS_TIMEOUT and the kernel returns. */
-DLB_API int dlb_p2p_barrier(const void* const* peer_signals, int world, int my_rank, uint32_t number, uint64_t limit_ns,
+ * store to); `counter` is this rank's own count of barriers on these words (one 32-bit word in device memory, zero
+ * at start): the kernel advances it, so a launch replayed from a CUDA graph keeps counting; every rank must run the
+ * same sequence of barriers.  The wait is bounded by `limit_ns`: on expiry *status becomes DLB_STATUS_TIMEOUT and the
+ * kernel returns. */
+DLB_API int dlb_p2p_barrier(const void* const* peer_signals, int world, int my_rank, uint32_t* counter, uint64_t limit_ns,
                     int32_t* status, void* stream);
+
+/* Low-latency (decode) exchange on the masked layout [E_local, rows_per_expert, k], in place of
+ * Buffer.low_latency_dispatch / low_latency_combine (dlblas/layers/moe/token_dispatcher.py:496-535, 567-582), with no
+ * host round trip: dlb_p2p_all_gather_small shares the per-expert pair counts (`bytes` of this rank's vector land in
+ * slot "my rank" of every peer's array), dlb_p2p_ll_quant_push quantises each token once
+ * (per_token_group_quant_fp8 arithmetic) and stores it for every routed slot f into row pair_row[f] of rank
+ * pair_rank[f] (negative: dropped), and dlb_p2p_push_rows_indexed sends row i of the experts' output to row
+ * row_pos[i] of rank row_rank[i] (negative: not sent). */
+DLB_API int dlb_p2p_all_gather_small(const void* src, int64_t bytes, int world, int my_rank, const void* const* peer_dst,
+                             void* stream);
+DLB_API int dlb_p2p_ll_quant_push(const void* x, int x_dtype, int64_t tokens, int64_t k, int64_t ldx, int mode, float eps,
+                          const int32_t* pair_rank, const int32_t* pair_row, int top_k, int world,
+                          const void* const* peer_q, const void* const* peer_scales, void* stream);
+DLB_API int dlb_p2p_push_rows_indexed(const void* src, int64_t row_bytes, int64_t rows, const int32_t* row_rank,
+                              const int32_t* row_pos, int world, const void* const* peer_dst, void* stream);
 
 /* ---- 16-bit grouped GEMM -----------------------------------------------------------------
  * m_grouped_gemm with trans_b = True (dlblas/kernels/grouped_gemm/BF16/m_grouped_gemm.py:235-352):

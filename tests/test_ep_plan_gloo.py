@@ -139,3 +139,70 @@ def test_single_rank_plan_without_process_group():
     sp = td.make_single_rank_plan(torch.tensor([1, 2, 0, 1]), 6, 8)
     assert sp.masked_m.tolist() == [1, 2, 0, 1] and sp.num_send == sp.num_recv == 6
     assert sp.recv_dst.tolist() == [0, 8, 9, 24, -1, -1]
+
+
+def test_host_free_low_latency_plan_round_trip():
+    """The index arithmetic of the peer-to-peer low-latency exchange, with the ranks emulated in one process: every
+    sent pair lands in a distinct row of its expert's block on the owner, the block is filled without holes in
+    (source rank, rank inside the source) order, and the owner's return addresses lead back to the pair's own row
+    of the source's return buffer.  Includes unrouted slots, an empty expert and an overfull block."""
+    from dlblas_b200.layers.moe.token_dispatcher import make_low_latency_p2p_plan
+    for w, e, k, tokens, rpe in [(4, 16, 4, [7, 0, 12, 5], 16), (2, 8, 2, [9, 9], 4), (8, 32, 8, [3] * 8, 24)]:
+        nle = e // w
+        g = torch.Generator().manual_seed(w * 100 + e)
+        ids, rank_in, counts = [], [], []
+        for r in range(w):
+            t = tokens[r]
+            x = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]) if t else torch.zeros(0, k).long()
+            x[x == 1] = 0                                             # expert 1 stays empty, expert 0 is crowded
+            if t:
+                x[0, 0] = -1                                          # a slot without an expert
+            flat = x.reshape(-1)
+            rk = torch.full_like(flat, -1)
+            seen = {}
+            for f, ex in enumerate(flat.tolist()):
+                if ex >= 0:
+                    rk[f] = seen.get(ex, 0)
+                    seen[ex] = rk[f] + 1
+            ids.append(x)
+            rank_in.append(rk.to(torch.int32))
+            counts.append(torch.bincount(flat[flat >= 0], minlength=e))
+        c = torch.stack(counts).to(torch.int64)
+        plans = [make_low_latency_p2p_plan(c, r, nle, rpe, ids[r], rank_in[r]) for r in range(w)]
+        # dispatch: every owner's masked layout records (source, flat pair index)
+        layout = [dict() for _ in range(w)]
+        for r in range(w):
+            pair_rank, pair_row, pair_pos, sent, _, _, _ = plans[r]
+            flat = ids[r].reshape(-1)
+            for f in range(flat.numel()):
+                if flat[f] < 0:
+                    assert not sent[f] and pair_rank[f] == -1 and pair_pos[f] == -1
+                    continue
+                if not sent[f]:
+                    continue
+                owner, row = int(pair_rank[f]), int(pair_row[f])
+                assert owner == int(flat[f]) // nle and row // rpe == int(flat[f]) % nle
+                assert row not in layout[owner], "two pairs in one row"
+                layout[owner][row] = (r, f)
+        for o in range(w):
+            _, _, _, _, masked_m, row_rank, row_pos = plans[o]
+            total = c[:, o * nle:(o + 1) * nle].sum(0)
+            assert torch.equal(masked_m.long(), total.clamp(max=rpe))
+            for le in range(nle):
+                rows = [layout[o].get(le * rpe + i) for i in range(rpe)]
+                filled = [x for x in rows if x is not None]
+                assert rows[:len(filled)] == filled and len(filled) == int(masked_m[le])   # no holes
+                assert filled == sorted(filled)                                              # source, then rank order
+                for i in range(rpe):
+                    rr = int(row_rank[le * rpe + i])
+                    if i < int(total[le]):
+                        assert rr >= 0
+                    else:
+                        assert rr == -1
+                    if i < len(filled):
+                        src, f = filled[i]
+                        assert rr == src and int(row_pos[le * rpe + i]) == int(plans[src][2][f])
+        for r in range(w):                                            # return rows of a source are distinct and dense
+            pos = plans[r][2][plans[r][3]]
+            assert pos.numel() == torch.unique(pos).numel()
+            assert pos.numel() == 0 or int(pos.max()) < int(c[r].sum())

@@ -46,7 +46,8 @@ def _worker(rank, world, port, ret):
         sl = slice(rank * nle, (rank + 1) * nle)
         local = [w13[sl].to(dev), w13s[sl].to(dev), w2[sl].to(dev), w2s[sl].to(dev)]
         os.environ["DLBLAS_EP_MAX_TOKENS"] = "256"
-        for backend, low_latency in (("p2p", False), ("p2p-chunked", False), ("nccl", False), ("nccl", True)):
+        for backend, low_latency in (("p2p", False), ("p2p-chunked", False), ("nccl", False), ("nccl", True),
+                                     ("p2p", True)):
             # two token chunks on two streams (ranks hold 96 and 128 tokens: chunks of 48 / 64)
             os.environ["DLBLAS_EP_MIN_CHUNK_ROWS"] = "32" if backend == "p2p-chunked" else "1024"
             os.environ["DLBLAS_EP_CHUNKS"] = "2" if backend == "p2p-chunked" else "1"
@@ -55,8 +56,12 @@ def _worker(rank, world, port, ret):
             backend = backend.split("-")[0]
             os.environ["DLBLAS_EP_BACKEND"] = backend
             layer = build_deepep_moe(low_latency, world, dist.group.WORLD, e, h, 128, k, torch.bfloat16)
-            assert (getattr(layer, "p2p_dispatcher", None) is not None) == (backend == "p2p")
-            if backend == "p2p":
+            if low_latency:
+                assert type(layer.token_dispatcher).__name__ == ("TokenDispatcherLowLatencyP2P" if backend == "p2p"
+                                                                 else "TokenDispatcherLowLatency")
+            else:
+                assert (getattr(layer, "p2p_dispatcher", None) is not None) == (backend == "p2p")
+            if backend == "p2p" and not low_latency:
                 assert len(layer.p2p_chunks) == (2 if os.environ["DLBLAS_EP_MIN_CHUNK_ROWS"] == "32" else 1)
             for _ in range(3):                      # repeated steps reuse the symmetric buffers
                 out = layer.forward(x.to(dev), ow.to(dev), oids.to(dev), *local)
@@ -133,8 +138,15 @@ def _worker_async_api(rank, world, port, ret):
         normal.wait(r2[5])
         assert torch.equal(r2[0][0].view(torch.uint8), recv_x[0].view(torch.uint8)) and torch.equal(r2[1], recv_idx)
 
-        low = build_deepep_moe(True, world, dist.group.WORLD, e, h, 128, k, torch.bfloat16)
-        whole = low.forward(x, w, ids, *local)
+        outs = {}
+        for ll_backend in ("nccl", "p2p"):
+            os.environ["DLBLAS_EP_BACKEND"] = ll_backend
+            low = build_deepep_moe(True, world, dist.group.WORLD, e, h, 128, k, torch.bfloat16)
+            outs[ll_backend] = low.forward(x, w, ids, *local)
+            outs[ll_backend] = low.forward(x, w, ids, *local)        # a second step reuses the symmetric buffers
+        _C.check_status(dev)
+        assert torch.equal(outs["nccl"], outs["p2p"]), "the two low-latency exchanges give different bits"
+        whole = outs["p2p"]
         packed, masked_m, handle, ev, hook = low.dispatch_async(x, ids, e, True, True)
         low.wait(ev)
         hook()
