@@ -182,6 +182,12 @@ class FusedMoENormal:
         backend = os.environ.get("DLBLAS_EP_BACKEND", "p2p" if ep_size > 1 else "nccl").lower()
         self.p2p_dispatcher = None
         self.p2p_chunks = []
+        # Optional callables for work that needs local data only (e.g. a shared expert's GEMMs): `during_dispatch`
+        # is called after this rank's tokens have been pushed and before the wait for the peers' tokens,
+        # `during_combine` after the results have been pushed back and before the wait for the peers' results, so
+        # the kernels they enqueue run while the other ranks' rows are in flight (peer-to-peer backend only).
+        self.during_dispatch = None
+        self.during_combine = None
         if backend == "p2p" and ep_size > 1:
             max_tokens = int(os.environ.get("DLBLAS_EP_MAX_TOKENS", "8192"))
             chunks = max(1, int(os.environ.get("DLBLAS_EP_CHUNKS", "1")))
@@ -200,13 +206,15 @@ class FusedMoENormal:
             self._chunk_streams = [torch.cuda.Stream() for _ in range(chunks - 1)]
 
     def _p2p_experts(self, d, hs, topk_ids, topk_weights, up_weights, up_scale, down_weights, down_scale):
-        (rq, rs), rids, rw = d.dispatch_from_hidden(hs, topk_ids, topk_weights, self.block_size)
+        (rq, rs), rids, rw = d.dispatch_from_hidden(hs, topk_ids, topk_weights, self.block_size,
+                                                    while_in_flight=self.during_dispatch)
         fused = os.environ.get("DLBLAS_EP_FUSED_COMBINE", "1") == "1"
         out_rows = moe_expert_forward(None, rq, rs, up_weights, up_scale, down_weights, down_scale, rw, rids,
                                       topk_ids.shape[1], hs.dtype, 0, self.num_local_experts,
                                       _C.QUANT_DIV_EPS, skip_unrouted_rows=True, return_slot_rows=fused)
         if fused:
-            return d.combine_slots(out_rows, rids)      # sum over a row's local slots while pushing it back
+            # sum over a row's local slots while pushing it back
+            return d.combine_slots(out_rows, rids, while_in_flight=self.during_combine)
         return d.combine(out_rows)
 
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.LongTensor,

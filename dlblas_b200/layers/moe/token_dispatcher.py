@@ -653,6 +653,11 @@ class TokenDispatcherP2P:
         self.recv_counts = self._sym.region("counts", 256).view(torch.int32)
         self.comb = self._sym.region("comb", rows * h * 2).view(params_dtype).view(rows, h)
         self.recv_counts.zero_()
+        # constants of the combine, built once
+        dev = self._sym.device
+        self._region_base = (torch.arange(w, device=dev, dtype=torch.int32) * self.region_rows)[None, :]
+        self._minus_one = torch.full((1, 1), -1, dtype=torch.int32, device=dev)
+        self._ones = torch.ones(self.region_rows, w, dtype=torch.float32, device=dev)
         torch.cuda.synchronize()
         dist.barrier(group=group)
         self.handle = None
@@ -667,9 +672,11 @@ class TokenDispatcherP2P:
         self._sym.resync()
 
     def dispatch_from_hidden(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
-                             block_size: int = 128):
+                             block_size: int = 128, while_in_flight=None):
         """Returns ((recv_q, recv_s), recv_ids, recv_weights): `world * max_tokens_per_rank` rows, local
-        expert ids with -1 for unused rows and for slots owned by other ranks."""
+        expert ids with -1 for unused rows and for slots owned by other ranks.  `while_in_flight`, if given, is
+        called between this rank's pushes and the barrier that waits for the peers': kernels it enqueues (work on
+        local data only) run while the other ranks' rows are still crossing NVLink."""
         assert block_size == 128
         t, k = topk_idx.shape
         # checked before anything is pushed or signalled: a rank that raises here has sent nothing; its peers'
@@ -688,6 +695,8 @@ class TokenDispatcherP2P:
             _C.ptr(hidden_states), _C.dtype_code(hidden_states.dtype), t, hidden_states.shape[1],
             hidden_states.stride(0), _C.QUANT_DIV_EPS, 1e-10, _C.ptr(within), w, self.rank, self.region_rows,
             p["q"], p["s"], p["meta"], _C.ptr(meta), self.meta_ints, p["counts"], _C.ptr(counts), _C.stream(dev)))
+        if while_in_flight is not None:
+            while_in_flight()
         self.barrier(0)
         recv_ids = torch.empty(self.rows, k, dtype=torch.int64, device=dev)
         recv_w = torch.empty(self.rows, k, dtype=torch.float32, device=dev)
@@ -708,7 +717,7 @@ class TokenDispatcherP2P:
                                            self._peers["comb"], _C.stream(dev)))
         return self._finish_combine(within, t, out_rows.dtype, dev)
 
-    def combine_slots(self, slot_rows: torch.Tensor, recv_ids: torch.Tensor) -> torch.Tensor:
+    def combine_slots(self, slot_rows: torch.Tensor, recv_ids: torch.Tensor, while_in_flight=None) -> torch.Tensor:
         """slot_rows: [world * max_tokens_per_rank * k, H] weighted results of the individual (row, slot) pairs,
         recv_ids int64 [rows, k] the local expert ids from `dispatch_from_hidden`.  Sums a row's slots and
         stores the sum into the source rank's buffer in one kernel (no intermediate [rows, H] tensor)."""
@@ -720,14 +729,15 @@ class TokenDispatcherP2P:
         _C.check(_C.lib().dlb_p2p_sum_push(_C.ptr(slot_rows), _C.dtype_code(slot_rows.dtype), _C.ptr(recv_ids), k,
                                           self.hidden_size, _C.ptr(self.recv_counts), w, self.rank, self.region_rows,
                                           self._peers["comb"], _C.stream(dev)))
-        return self._finish_combine(within, t, slot_rows.dtype, dev)
+        return self._finish_combine(within, t, slot_rows.dtype, dev, while_in_flight)
 
-    def _finish_combine(self, within, t, dtype, dev):
+    def _finish_combine(self, within, t, dtype, dev, while_in_flight=None):
         w = self.world_size
+        if while_in_flight is not None:
+            while_in_flight()
         self.barrier(1)
-        base = (torch.arange(w, device=dev, dtype=torch.int32) * self.region_rows)[None, :]
-        idx = torch.where(within >= 0, within + base, torch.full_like(within, -1)).contiguous()
-        ones = torch.ones(t, w, dtype=torch.float32, device=dev)
+        idx = torch.where(within >= 0, within + self._region_base, self._minus_one).contiguous()
+        ones = self._ones[:t]
         out = torch.empty(t, self.hidden_size, dtype=dtype, device=dev)
         # out[t] = sum over the ranks the token visited, in rank order (fp32 accumulation)
         ops.ep_gather(self.comb, idx, ones, idx, out)
