@@ -51,6 +51,15 @@ struct Args16 {
   const int4* tiles;     // nullptr: one group, M tiles derived from m
   int m, n, k_bytes;
   int num_m_tiles_static, num_n_tiles;
+  // Groups along the reduction dimension (k_grouped_gemm): tile {g, row0, rows} multiplies rows [row0, row0 + rows) of
+  // A by rows [n0, ...) of B over the K blocks of group g, kseg[g] = {first K block, number of K blocks (>= 1)}, and
+  // writes rows g * c_group_rows + row0 ... of C.  Both operands are then stored K block by K block, A as
+  // [k blocks, m, 64] and B as [k blocks, n, 64], so a tile's K block is one contiguous run of 128-byte rows.
+  // Otherwise kseg is null, the operands are [rows, k], the K range is the whole K, B holds one [n, k] matrix per group
+  // (b_group_rows = n) and c_group_rows = 0.
+  const int2* kseg;
+  int b_group_rows;
+  long long c_group_rows;
   uint32_t idesc;
   int* status;
   unsigned long long timeout_cycles;
@@ -187,8 +196,13 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     bool ok = true;
     for (int t = worker; t < total_tiles && ok; t += workers) {
       const Tile16 ti = decode16<CTAS>(g, t);
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+      const int2 ks = g.kseg != nullptr ? __ldg(g.kseg + ti.e) : make_int2(0, kblocks);
+      const bool blocked = g.kseg != nullptr;
+      for (int kb = 0; kb < ks.y; ++kb, ++it) {
         const int s = it % STAGES;
+        const int kx = blocked ? 0 : kb * UMMA_BK_BYTES;
+        const int a_row = ti.row0 + (blocked ? (ks.x + kb) * g.m : 0);
+        const int b_row = ti.n0 + (blocked ? (ks.x + kb) * g.n : ti.e * g.b_group_rows);
         if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, abort_flag, limit)) {
           ok = false;
           break;
@@ -199,14 +213,14 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           const uint32_t lead_full = mapa(full_bar(s), 0);
           if (elect_one()) {
             if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);      // the loads of both CTAs
-            tma_load_2d_pair(a_dst, &tmap_a, kb * UMMA_BK_BYTES, ti.row0 + (int)rank * BM, lead_full);
-            tma_load_2d_pair(b_dst, &tmap_b, kb * UMMA_BK_BYTES, ti.e * g.n + ti.n0 + (int)rank * (BN / 2), lead_full);
+            tma_load_2d_pair(a_dst, &tmap_a, kx, a_row + (int)rank * BM, lead_full);
+            tma_load_2d_pair(b_dst, &tmap_b, kx, b_row + (int)rank * (BN / 2), lead_full);
           }
         } else if (elect_one()) {
           mbar_expect_tx(full_bar(s), STAGE_BYTES);
-          tma_load_2d(a_dst, &tmap_a, kb * UMMA_BK_BYTES, ti.row0, full_bar(s));
-          tma_load_2d(b_dst, &tmap_b, kb * UMMA_BK_BYTES, ti.e * g.n + ti.n0, full_bar(s));
-          tma_load_2d(b_dst + 128 * UMMA_BK_BYTES, &tmap_b, kb * UMMA_BK_BYTES, ti.e * g.n + ti.n0 + 128, full_bar(s));
+          tma_load_2d(a_dst, &tmap_a, kx, a_row, full_bar(s));
+          tma_load_2d(b_dst, &tmap_b, kx, b_row, full_bar(s));
+          tma_load_2d(b_dst + 128 * UMMA_BK_BYTES, &tmap_b, kx, b_row + 128, full_bar(s));
         }
         __syncwarp();
       }
@@ -226,7 +240,8 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         break;
       }
       const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+      const int nkb = g.kseg != nullptr ? __ldg(g.kseg + decode16<CTAS>(g, t).e).y : kblocks;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = it % STAGES;
         if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, abort_flag, limit)) {
           ok = false;
@@ -242,13 +257,13 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             for (int kk = 0; kk < UMMA_BK_BYTES / 32; ++kk)
               tc_mma_f16_pair(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             tc_commit_pair(empty_bar(s));                          // frees the stage in both CTAs
-            if (kb == kblocks - 1) tc_commit_pair(tfull_bar(b));   // both CTAs' drain warps
+            if (kb == nkb - 1) tc_commit_pair(tfull_bar(b));       // both CTAs' drain warps
           } else {
 #pragma unroll
             for (int kk = 0; kk < UMMA_BK_BYTES / 32; ++kk)
               tc_mma_f16(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             tc_commit(empty_bar(s));
-            if (kb == kblocks - 1) tc_commit(tfull_bar(b));
+            if (kb == nkb - 1) tc_commit(tfull_bar(b));
           }
         }
         __syncwarp();
@@ -282,7 +297,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       for (int i = 0; i < 2; ++i) {
         const int row = ew * 64 + i * 32 + lane;
         if (row < my_rows)
-          bulk_store(reinterpret_cast<T*>(g.c) + ((long long)my_row0 + row) * g.ldc + ti.n0,
+          bulk_store(reinterpret_cast<T*>(g.c) + ((long long)my_row0 + row + ti.e * g.c_group_rows) * g.ldc + ti.n0,
                      smem_u32(staging + row * STAGING_ROW_BYTES), bytes);
       }
       bulk_commit();
@@ -398,6 +413,123 @@ int launch16(const CUtensorMap& ma, const CUtensorMap& mb, const Args16& g, int 
   return DLB_OK;
 }
 
+// ---- groups along the reduction dimension (k_grouped_gemm) ----------------------------------------------------------
+// C[g] = A_g^T B_g with A [k_total, m], B [k_total, n] row-major and group g owning rows [start_g, start_g + size_g).
+// The tensor cores want both operands K-major, so each operand is transposed once into K blocks of 64 elements,
+// [k blocks, m or n, 64]: every group's K range starts on a block boundary and is zero-filled up to the next one, and
+// an empty group gets one block of zeros so that its tiles still run and write zeros.  One K block of a tile is then
+// 128 or 256 consecutive 128-byte rows (a [m, k] layout with rows megabytes apart measured 40 % slower at
+// k_total = 650 k: every row of a TMA box on its own page).
+
+struct KSpan {
+  long long start;   // first row of the group in A and B
+  long long size;    // its rows, clipped to what k_total leaves
+};
+
+// One block.  Thread 0 scans the group sizes; all threads then write the tile list {group, row0, rows}.
+__global__ void k_group_plan_kernel(const long long* __restrict__ sizes, int groups, long long k_total, int m,
+                                    int tile_rows, int2* __restrict__ kseg, KSpan* __restrict__ span,
+                                    int4* __restrict__ tiles) {
+  if (threadIdx.x == 0) {
+    long long run = 0, kal = 0;
+    for (int g = 0; g < groups; ++g) {
+      long long sz = sizes[g];
+      sz = sz < 0 ? 0 : sz;
+      sz = sz > k_total - run ? k_total - run : sz;
+      const long long nkb = sz == 0 ? 1 : (sz + 63) / 64;
+      span[g] = KSpan{run, sz};
+      kseg[g] = make_int2((int)kal, (int)nkb);
+      run += sz;
+      kal += nkb;
+    }
+  }
+  const int m_tiles = (m + tile_rows - 1) / tile_rows;
+  if (threadIdx.x == 0) tiles[0] = make_int4(groups * m_tiles, 0, 0, 0);
+  for (int i = threadIdx.x; i < groups * m_tiles; i += blockDim.x) {
+    const int g = i / m_tiles, t = i - g * m_tiles;
+    tiles[1 + i] = make_int4(g, t * tile_rows, min(tile_rows, m - t * tile_rows), 0);
+  }
+}
+
+// x [k_total, cols] (16-bit elements, row stride ldx) -> xt [k blocks, cols, 64].  Block (bx, by) produces K block bx
+// of rows [64 by, 64 by + 64), 8 KB of contiguous output: one 64 x 64 tile through shared memory, 32-bit accesses
+// both ways.
+__global__ void __launch_bounds__(256)
+transpose_align_kernel(const uint16_t* __restrict__ x, long long ldx, int cols, const int2* __restrict__ kseg,
+                       const KSpan* __restrict__ span, int groups, uint16_t* __restrict__ xt) {
+  __shared__ uint32_t tile[64][33];
+  const int blk = blockIdx.x;
+  int lo = 0, hi = groups - 1;                      // the last group that starts at or before this K block
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (__ldg(&kseg[mid]).x <= blk) lo = mid; else hi = mid - 1;
+  }
+  const int2 ks = __ldg(&kseg[lo]);
+  if (blk - ks.x >= ks.y) return;                   // past the last group's blocks: nothing reads there
+  const long long k0 = 64ll * (blk - ks.x);
+  const KSpan sp = span[lo];
+  const int valid = (int)max(0ll, min(64ll, sp.size - k0));
+  const int m0 = 64 * blockIdx.y;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int kl = ty + 8 * i;
+    uint32_t v = 0;
+    if (kl < valid && m0 + 2 * tx < cols)
+      v = *reinterpret_cast<const uint32_t*>(x + (sp.start + k0 + kl) * ldx + m0 + 2 * tx);
+    tile[kl][tx] = v;
+  }
+  __syncthreads();
+  const uint16_t* t16 = reinterpret_cast<const uint16_t*>(&tile[0][0]);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int ml = ty + 8 * i;
+    if (m0 + ml < cols) {
+      const uint32_t a = t16[(2 * tx) * 66 + ml], b = t16[(2 * tx + 1) * 66 + ml];
+      *reinterpret_cast<uint32_t*>(xt + ((long long)blk * cols + m0 + ml) * 64 + 2 * tx) = a | (b << 16);
+    }
+  }
+}
+
+// Maps, arguments and launch shared by the two entry points.  a: [a_map_rows, k] and b: [b_map_rows, k] 16-bit,
+// K-major, as the tensor maps see them; m rows of A (per K block when kseg is given) meet n rows of B.
+static int run_gemm16(const void* a, int64_t a_map_rows, const void* b, int64_t b_map_rows, int dtype, int64_t m,
+                      int64_t n, int64_t k, const int2* kseg, int b_group_rows, long long c_group_rows,
+                      const int32_t* tiles, int max_tiles, int tile_rows, void* c, int64_t ldc, int32_t* status,
+                      void* stream) {
+  int rc = check_device();
+  if (rc != DLB_OK) return rc;
+  CUtensorMap ma, mb;
+  if ((rc = make_map(&ma, a, (uint64_t)a_map_rows, (uint64_t)(2 * k))) != DLB_OK) return rc;
+  if ((rc = make_map(&mb, b, (uint64_t)b_map_rows, (uint64_t)(2 * k))) != DLB_OK) return rc;
+  Args16 g = {};
+  g.c = c;
+  g.ldc = ldc;
+  g.tiles = reinterpret_cast<const int4*>(tiles);
+  g.m = (int)m;
+  g.n = (int)n;
+  g.k_bytes = (int)(2 * k);
+  g.kseg = kseg;
+  g.b_group_rows = b_group_rows;
+  g.c_group_rows = c_group_rows;
+  const int ctas = tile_rows / BM;
+  g.num_m_tiles_static = (int)ceil_div(m, (int64_t)tile_rows);
+  g.num_n_tiles = (int)ceil_div(n, (int64_t)BN);
+  g.idesc = make_idesc16(dtype == DLB_BF16 ? 1u : 0u, ctas);
+  g.status = status;
+  g.timeout_cycles = wait_limit_cycles(DEFAULT_TIMEOUT_CYCLES);
+  const int workers = sm_count() / ctas;
+  const long long total = (long long)(tiles != nullptr ? max_tiles : g.num_m_tiles_static) * g.num_n_tiles;
+  const int grid = ctas * (int)(total < workers ? total : workers);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (ctas == 2) {
+    if (dtype == DLB_BF16) return launch16<__nv_bfloat16, 2>(ma, mb, g, grid, st);
+    return launch16<__half, 2>(ma, mb, g, grid, st);
+  }
+  if (dtype == DLB_BF16) return launch16<__nv_bfloat16, 1>(ma, mb, g, grid, st);
+  return launch16<__half, 1>(ma, mb, g, grid, st);
+}
+
 }  // namespace
 }  // namespace dlb
 
@@ -422,32 +554,66 @@ extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, i
   DLB_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 16 == 0) &&
                   ((uintptr_t)tiles % 16 == 0),
               DLB_ERR_INVALID, "grouped_gemm_16bit: a, b, c and tiles must be 16-byte aligned");
+  return run_gemm16(a, rows, b, (int64_t)num_groups * n, dtype, rows, n, k, nullptr, (int)n, 0, tiles, max_tiles,
+                    tile_rows, c, ldc, status, stream);
+}
+
+// Workspace of dlb_k_grouped_gemm_16bit, in bytes: both transposed operands, the K ranges and the tile list.
+static int64_t k_grouped_kal(int64_t k_total, int num_groups) { return (k_total + 63) / 64 * 64 + 64ll * num_groups; }
+
+extern "C" int64_t dlb_k_grouped_gemm_workspace_bytes(int64_t k_total, int64_t m, int64_t n, int num_groups,
+                                                      int tile_rows) {
+  if (k_total < 0 || m <= 0 || n <= 0 || num_groups <= 0 || (tile_rows != 128 && tile_rows != 256)) return -1;
+  const int64_t kal = k_grouped_kal(k_total, num_groups);
+  const int64_t m_tiles = ceil_div(m, (int64_t)tile_rows);
+  return 2 * kal * (m + n) + 16 * (1 + num_groups * m_tiles) + 8 * (int64_t)num_groups + 16 * (int64_t)num_groups;
+}
+
+extern "C" int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t k_total, int64_t m, int64_t n,
+                                        const int64_t* group_sizes, int num_groups, int tile_rows, void* workspace,
+                                        int64_t workspace_bytes, void* c, int32_t* status, void* stream) {
+  DLB_REQUIRE(k_total >= 0 && m > 0 && n > 0 && num_groups > 0, DLB_ERR_INVALID,
+              "k_grouped_gemm_16bit: bad sizes k_total=%lld m=%lld n=%lld groups=%d", (long long)k_total, (long long)m,
+              (long long)n, num_groups);
+  DLB_REQUIRE(dtype == DLB_BF16 || dtype == DLB_F16, DLB_ERR_INVALID, "k_grouped_gemm_16bit: dtype must be bf16 or fp16");
+  DLB_REQUIRE(m % 8 == 0 && n % 8 == 0, DLB_ERR_INVALID,
+              "k_grouped_gemm_16bit: m=%lld and n=%lld must be multiples of 8 (16-byte rows)", (long long)m, (long long)n);
+  DLB_REQUIRE(tile_rows == 128 || tile_rows == 256, DLB_ERR_INVALID, "k_grouped_gemm_16bit: tile_rows must be 128 or 256");
+  const int64_t kal = k_grouped_kal(k_total, num_groups);
+  const int64_t m_tiles = ceil_div(m, (int64_t)tile_rows);
+  DLB_REQUIRE(kal / 64 * m < (1ll << 31) && kal / 64 * n < (1ll << 31) && num_groups * m_tiles < (1ll << 24),
+              DLB_ERR_INVALID, "k_grouped_gemm_16bit: size too large");
+  if (k_total == 0) {   // nothing to reduce over: every group is empty
+    DLB_REQUIRE(c != nullptr, DLB_ERR_INVALID, "k_grouped_gemm_16bit: null pointer");
+    return check_cuda(cudaMemsetAsync(c, 0, (size_t)(2 * num_groups * m * n), (cudaStream_t)stream),
+                      "cudaMemsetAsync(k_grouped_gemm_16bit, c)");
+  }
+  DLB_REQUIRE(a && b && c && group_sizes && workspace, DLB_ERR_INVALID, "k_grouped_gemm_16bit: null pointer");
+  DLB_REQUIRE(((uintptr_t)a % 4 == 0) && ((uintptr_t)b % 4 == 0) && ((uintptr_t)c % 16 == 0) &&
+                  ((uintptr_t)workspace % 128 == 0),
+              DLB_ERR_INVALID, "k_grouped_gemm_16bit: a, b must be 4-byte, c 16-byte and workspace 128-byte aligned");
+  DLB_REQUIRE(workspace_bytes >= dlb_k_grouped_gemm_workspace_bytes(k_total, m, n, num_groups, tile_rows), DLB_ERR_INVALID,
+              "k_grouped_gemm_16bit: workspace of %lld bytes is too small", (long long)workspace_bytes);
   int rc = check_device();
   if (rc != DLB_OK) return rc;
-  CUtensorMap ma, mb;
-  if ((rc = make_map(&ma, a, (uint64_t)rows, (uint64_t)(2 * k))) != DLB_OK) return rc;
-  if ((rc = make_map(&mb, b, (uint64_t)num_groups * (uint64_t)n, (uint64_t)(2 * k))) != DLB_OK) return rc;
-  Args16 g = {};
-  g.c = c;
-  g.ldc = ldc;
-  g.tiles = reinterpret_cast<const int4*>(tiles);
-  g.m = (int)rows;
-  g.n = (int)n;
-  g.k_bytes = (int)(2 * k);
-  const int ctas = tile_rows / BM;
-  g.num_m_tiles_static = (int)ceil_div(rows, (int64_t)tile_rows);
-  g.num_n_tiles = (int)ceil_div(n, (int64_t)BN);
-  g.idesc = make_idesc16(dtype == DLB_BF16 ? 1u : 0u, ctas);
-  g.status = status;
-  g.timeout_cycles = wait_limit_cycles(DEFAULT_TIMEOUT_CYCLES);
-  const int workers = sm_count() / ctas;
-  const long long total = (long long)(tiles != nullptr ? max_tiles : g.num_m_tiles_static) * g.num_n_tiles;
-  const int grid = ctas * (int)(total < workers ? total : workers);
+  uint8_t* w = reinterpret_cast<uint8_t*>(workspace);
+  uint16_t* at = reinterpret_cast<uint16_t*>(w);
+  uint16_t* bt = reinterpret_cast<uint16_t*>(w + 2 * kal * m);
+  int4* tiles = reinterpret_cast<int4*>(w + 2 * kal * (m + n));
+  KSpan* span = reinterpret_cast<KSpan*>(tiles + 1 + num_groups * m_tiles);
+  int2* kseg = reinterpret_cast<int2*>(span + num_groups);
   cudaStream_t st = (cudaStream_t)stream;
-  if (ctas == 2) {
-    if (dtype == DLB_BF16) return launch16<__nv_bfloat16, 2>(ma, mb, g, grid, st);
-    return launch16<__half, 2>(ma, mb, g, grid, st);
-  }
-  if (dtype == DLB_BF16) return launch16<__nv_bfloat16, 1>(ma, mb, g, grid, st);
-  return launch16<__half, 1>(ma, mb, g, grid, st);
+  k_group_plan_kernel<<<1, 256, 0, st>>>(reinterpret_cast<const long long*>(group_sizes), num_groups, k_total, (int)m,
+                                         tile_rows, kseg, span, tiles);
+  if ((rc = check_cuda(cudaGetLastError(), "k_group_plan_kernel")) != DLB_OK) return rc;
+  count_launch();
+  const dim3 ga((unsigned)(kal / 64), (unsigned)ceil_div(m, (int64_t)64)), gb((unsigned)(kal / 64), (unsigned)ceil_div(n, (int64_t)64));
+  transpose_align_kernel<<<ga, 256, 0, st>>>(reinterpret_cast<const uint16_t*>(a), m, (int)m, kseg, span, num_groups, at);
+  if ((rc = check_cuda(cudaGetLastError(), "transpose_align_kernel(a)")) != DLB_OK) return rc;
+  count_launch();
+  transpose_align_kernel<<<gb, 256, 0, st>>>(reinterpret_cast<const uint16_t*>(b), n, (int)n, kseg, span, num_groups, bt);
+  if ((rc = check_cuda(cudaGetLastError(), "transpose_align_kernel(b)")) != DLB_OK) return rc;
+  count_launch();
+  return run_gemm16(at, kal / 64 * m, bt, kal / 64 * n, dtype, m, n, 64, kseg, 0, m, reinterpret_cast<const int32_t*>(tiles),
+                    (int)(num_groups * m_tiles), tile_rows, c, n, status, stream);
 }

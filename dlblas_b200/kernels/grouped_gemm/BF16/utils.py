@@ -15,3 +15,19 @@ def gmm(a, b, batch_sizes, trans_b=False):
 def allclose(x, y, pct=2.0):
     mask = torch.isclose(x, y, rtol=1e-5)
     return float((mask.numel() - mask.sum()) / mask.numel() * 100) <= pct
+
+
+def gmm_dw(a, b, batch_sizes):
+    """Group-by-group `a_g.T @ b_g` over row groups of the shared leading dimension: the ground truth of the
+    reference's k_grouped_gemm test (tests/kernels/grouped_gemm/BF16/test_k_grouped_gemm.py:10-28)."""
+    out = a.new_empty(batch_sizes.numel(), a.shape[1], b.shape[1])
+    start = 0
+    for g, size in enumerate(batch_sizes.tolist()):
+        out[g] = a[start:start + size].t() @ b[start:start + size]
+        start += size
+    return out
+
+
+def row_max_normalization(tensor):
+    """Each row divided by its largest magnitude (dlblas/kernels/grouped_gemm/BF16/utils.py:113-116)."""
+    return tensor / (tensor.abs().max(dim=-1).values + 1e-9).unsqueeze(-1)

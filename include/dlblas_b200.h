@@ -270,6 +270,19 @@ DLB_API int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, int6
                            int64_t k, const int32_t* tiles, int max_tiles, int tile_rows, void* c, int64_t ldc,
                            int32_t* status, void* stream);
 
+/* k_grouped_gemm (dlblas/kernels/grouped_gemm/BF16/k_grouped_gemm.py:126-176, :254-330): groups along the reduction
+ * dimension.  a [k_total, m] and b [k_total, n] row-major bf16 or fp16; group g owns the next group_sizes[g] rows of
+ * both (int64 on the device; the sizes are clipped to k_total); c [num_groups, m, n] of the same type with
+ * c[g] = a_g^T b_g, fp32 accumulation, zeros for an empty group.  m and n multiples of 8.  The call transposes both
+ * operands into `workspace` (dlb_k_grouped_gemm_workspace_bytes bytes, 128-byte aligned, device memory) as blocks of
+ * 64 K elements, every group's K range padded with zeros to whole blocks, and runs the tcgen05 kernel over
+ * [group, m tile, n tile];
+ * tile_rows as for dlb_grouped_gemm_16bit.  Nothing synchronises with the host. */
+DLB_API int64_t dlb_k_grouped_gemm_workspace_bytes(int64_t k_total, int64_t m, int64_t n, int num_groups, int tile_rows);
+DLB_API int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t k_total, int64_t m, int64_t n,
+                             const int64_t* group_sizes, int num_groups, int tile_rows, void* workspace,
+                             int64_t workspace_bytes, void* c, int32_t* status, void* stream);
+
 /* ---- training-side permutation (dlblas/kernels/permute/moe_triton_kernels.py) ------------------
  * row_id_map int32 [top_k * tokens], k-major: destination row of (token, slot) in the permuted tensor, -1 for
  * unrouted slots.  Permute forward is dlb_sort_by_expert + dlb_permute_rows.

@@ -617,3 +617,16 @@ def m_grouped_gemm(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tenso
         out.append((a[start:start + size].to(torch.float32) @ rhs.to(torch.float32)).to(a.dtype))
         start += size
     return torch.cat(out) if out else a.new_empty(0, b.shape[1] if trans_b else b.shape[2])
+
+
+def k_grouped_gemm(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tensor) -> torch.Tensor:
+    """dlblas/kernels/grouped_gemm/BF16/k_grouped_gemm.py:126-176 against its ground truth `gmm_dw`
+    (tests/kernels/grouped_gemm/BF16/test_k_grouped_gemm.py:10-28): c[g] = a_g^T b_g over row groups of the shared
+    leading dimension, fp32 accumulation of 16-bit operands, one rounding to the operand type; zeros for an empty
+    group."""
+    out = a.new_zeros(size_per_group.numel(), a.shape[1], b.shape[1])
+    start = 0
+    for g, size in enumerate(size_per_group.tolist()):
+        out[g] = (a[start:start + size].to(torch.float32).t() @ b[start:start + size].to(torch.float32)).to(a.dtype)
+        start += size
+    return out

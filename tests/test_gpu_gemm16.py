@@ -51,3 +51,51 @@ def test_m_grouped_gemm_large_and_empty():
     assert torch.equal(out, out1)                                # same sums in the same order
     empty = m_grouped_gemm(a[:0], b, torch.zeros(4, dtype=torch.int64, device=DEV), trans_b=True)
     assert empty.shape == (0, 1024)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("tile_rows", [128, 256])
+def test_k_grouped_gemm(dtype, tile_rows, monkeypatch):
+    monkeypatch.setenv("DLBLAS_GEMM16_TILE_ROWS", str(tile_rows))
+    from dlblas_b200 import _C
+    from dlblas_b200.kernels.grouped_gemm.BF16 import k_grouped_gemm
+    g = torch.Generator().manual_seed(17)
+    # ragged K ranges (not multiples of the 64-element K block), empty groups first / in the middle / last,
+    # m and n that are not multiples of the tile, a single group
+    for (sizes, m, n) in [([5, 0, 130, 64, 257], 264, 200), ([128, 128], 512, 256), ([1], 8, 8), ([0, 300, 211, 0], 136, 1096),
+                          ([0], 16, 24)]:
+        sz = torch.tensor(sizes, dtype=torch.int64)
+        k = int(sz.sum())
+        a = (torch.randn(k, m, generator=g) * 0.5).to(dtype)
+        b = (torch.randn(k, n, generator=g) * 0.5).to(dtype)
+        out = k_grouped_gemm(a.to(DEV), b.to(DEV), sz.to(DEV))
+        _C.check_status()
+        ref = O.k_grouped_gemm(a, b, sz)
+        assert out.shape == (len(sizes), m, n) and out.dtype == dtype
+        assert O.rel_frobenius(out.cpu(), ref) < 2e-3
+        assert float((out.cpu().float() - ref.float()).abs().max()) <= 2 ** -6 * max(float(ref.float().abs().max()), 1e-6)
+        for i, size in enumerate(sizes):
+            if size == 0:
+                assert not out[i].any()                          # an empty group writes zeros
+
+
+def test_k_grouped_gemm_like_the_reference_test():
+    # tests/kernels/grouped_gemm/BF16/test_k_grouped_gemm.py of the reference at a sixteenth of its K: random group
+    # sizes, row-max normalisation, rtol = atol = 0.01
+    import random
+    from dlblas_b200 import _C
+    from dlblas_b200.kernels.grouped_gemm.BF16 import k_grouped_gemm, utils
+    random.seed(3)
+    groups = 16
+    raw = [random.randint(0, 2 * 2560) for _ in range(groups)]
+    sizes = torch.tensor(raw, dtype=torch.int64, device=DEV)
+    k = int(sizes.sum())
+    g = torch.Generator(device=DEV).manual_seed(2)
+    for (m, n) in ((1536, 2048), (2048, 768)):
+        a = torch.randn(k, m, generator=g, device=DEV, dtype=torch.bfloat16)
+        b = torch.randn(k, n, generator=g, device=DEV, dtype=torch.bfloat16)
+        out = k_grouped_gemm(a, b, sizes)
+        _C.check_status()
+        ref = utils.gmm_dw(a, b, sizes.cpu())
+        torch.testing.assert_close(utils.row_max_normalization(out.float()), utils.row_max_normalization(ref.float()),
+                                   rtol=0.01, atol=0.01)
