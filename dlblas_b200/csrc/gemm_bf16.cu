@@ -58,6 +58,12 @@ struct Args16 {
   // Otherwise kseg is null, the operands are [rows, k], the K range is the whole K, B holds one [n, k] matrix per group
   // (b_group_rows = n) and c_group_rows = 0.
   const int2* kseg;
+  int group_m_tiles;   // m tiles per group when kseg is given
+  // Per-worker tile lists (a worker is a CTA or a pair): worker w runs tiles sched[w * sched_stride + i] for
+  // i < sched_count[w].  Null: worker w runs tiles w, w + workers, ...
+  const int* sched;
+  const int* sched_count;
+  int sched_stride;
   int b_group_rows;
   long long c_group_rows;
   uint32_t idesc;
@@ -93,10 +99,25 @@ __device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc
 struct Tile16 {
   int e, row0, rows, n0;
 };
+constexpr int KG_BAND = 8;   // n tiles per band in the tile order of k-grouped launches
+
 template <int CTAS> __device__ __forceinline__ Tile16 decode16(const Args16& g, int t) {
   Tile16 ti;
-  const int m_tile = t / g.num_n_tiles;
-  const int n_tile = t - m_tile * g.num_n_tiles;
+  int m_tile = t / g.num_n_tiles;
+  int n_tile = t - m_tile * g.num_n_tiles;
+  if (g.kseg != nullptr) {
+    // Every group has the same m x n grid of tiles.  Walk it in bands of KG_BAND n tiles, m tile by m tile inside a
+    // band: the tiles in flight at one time (one per CTA or pair) then cover about as many A row blocks as B row
+    // blocks, and a band of B stays in L2 while A streams past it (measured with ragged K ranges of up to 10 k:
+    // DRAM reads 12.2 -> see the profile of this kernel).
+    const int per_group = g.group_m_tiles * g.num_n_tiles;
+    const int grp = t / per_group, l = t - grp * per_group;
+    const int band = l / (g.group_m_tiles * KG_BAND), li = l - band * g.group_m_tiles * KG_BAND;
+    const int width = min(KG_BAND, g.num_n_tiles - band * KG_BAND);
+    const int mt = li / width;
+    m_tile = grp * g.group_m_tiles + mt;
+    n_tile = band * KG_BAND + (li - mt * width);
+  }
   if (g.tiles != nullptr) {
     const int4 v = __ldg(g.tiles + 1 + m_tile);
     ti.e = v.x;
@@ -151,6 +172,10 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   const int kblocks = (g.k_bytes + UMMA_BK_BYTES - 1) / UMMA_BK_BYTES;
   const int num_m_tiles = g.tiles != nullptr ? __ldg(reinterpret_cast<const int*>(g.tiles)) : g.num_m_tiles_static;
   const int total_tiles = num_m_tiles * g.num_n_tiles;
+  const int my_tiles = g.sched != nullptr ? __ldg(g.sched_count + worker)
+                                          : (worker < total_tiles ? (total_tiles - worker + workers - 1) / workers : 0);
+  const int* my_sched = g.sched != nullptr ? g.sched + (long long)worker * g.sched_stride : nullptr;
+  auto tile_at = [&](int i) { return my_sched != nullptr ? __ldg(my_sched + i) : worker + i * workers; };
   const unsigned long long limit = g.timeout_cycles;
 
   if (threadIdx.x == 0) {
@@ -194,7 +219,8 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   if (warp == PRODUCER_WARP) {
     uint32_t it = 0;
     bool ok = true;
-    for (int t = worker; t < total_tiles && ok; t += workers) {
+    for (int i = 0; i < my_tiles && ok; ++i) {
+      const int t = tile_at(i);
       const Tile16 ti = decode16<CTAS>(g, t);
       const int2 ks = g.kseg != nullptr ? __ldg(g.kseg + ti.e) : make_int2(0, kblocks);
       const bool blocked = g.kseg != nullptr;
@@ -233,7 +259,8 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   } else if (warp == MMA_WARP) {
     uint32_t it = 0, tile_no = 0;
     bool ok = true;
-    for (int t = worker; t < total_tiles && ok && rank == 0; t += workers, ++tile_no) {
+    for (int i = 0; i < my_tiles && ok && rank == 0; ++i, ++tile_no) {
+      const int t = tile_at(i);
       const int b = tile_no % TMEM_BUFS;
       if (!mbar_wait(tempty_bar(b), ((tile_no / TMEM_BUFS) & 1u) ^ 1u, abort_flag, limit)) {
         ok = false;
@@ -284,7 +311,8 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const int ew = warp - STORE_WARP0;
     uint32_t tile_no = 0;
     bool ok = true;
-    for (int t = worker; t < total_tiles && ok; t += workers, ++tile_no) {
+    for (int i = 0; i < my_tiles && ok; ++i, ++tile_no) {
+      const int t = tile_at(i);
       const Tile16 ti = decode16<CTAS>(g, t);
       if (!mbar_wait(staged_bar, tile_no & 1u, abort_flag, limit)) {
         ok = false;
@@ -315,7 +343,8 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint8_t* srow = staging + r * STAGING_ROW_BYTES + wg * 128 * 2;
     uint32_t tile_no = 0;
     bool ok = true;
-    for (int t = worker; t < total_tiles && ok; t += workers, ++tile_no) {
+    for (int i = 0; i < my_tiles && ok; ++i, ++tile_no) {
+      const int t = tile_at(i);
       const int b = tile_no % TMEM_BUFS;
       if (!mbar_wait(tfull_bar(b), (tile_no / TMEM_BUFS) & 1u, abort_flag, limit) ||
           !mbar_wait(sfree_bar, (tile_no & 1u) ^ 1u, abort_flag, limit)) {
@@ -451,6 +480,55 @@ __global__ void k_group_plan_kernel(const long long* __restrict__ sizes, int gro
   }
 }
 
+// Tile lists for the workers of the GEMM (one block, at least `workers` threads).  Tiles are handed out in tile order,
+// group by group, each to the worker that a greedy scheduler would find free first, with a tile's cost taken as its
+// K blocks (at least KG_MIN_COST, the part of a tile that does not shrink with K).  All tiles of a group cost the same,
+// so inside a group the order of the workers by the time they become free does not change: one ranking per group, tile
+// l of the group to the worker of rank l mod workers.  Tiles that follow one another in tile order (and share rows of A
+// or B) thus start at about the same time whatever the K ranges of the groups before them; handing tile t to worker
+// t mod workers lets the workers drift apart by whole tiles once the groups differ in K, and the operands were then
+// read from DRAM 4.4 times instead of 1.5 (K ranges uniform in 0 ... 10 k).
+constexpr int KG_MIN_COST = 8;
+
+__global__ void __launch_bounds__(256)
+k_group_schedule_kernel(const int2* __restrict__ kseg, int groups, int tiles_per_group, int workers,
+                        int* __restrict__ sched, int* __restrict__ sched_count, int sched_stride) {
+  __shared__ long long free_at[256];
+  __shared__ int count[256];
+  __shared__ int by_rank[256];
+  const int w = threadIdx.x;
+  if (w < workers) {
+    free_at[w] = 0;
+    count[w] = 0;
+  }
+  __syncthreads();
+  const int full = tiles_per_group / workers, rest = tiles_per_group - full * workers;
+  for (int g = 0; g < groups; ++g) {
+    int my_rank = 0;
+    if (w < workers) {
+      const long long mine = free_at[w];
+      for (int v = 0; v < workers; ++v) {
+        const long long other = free_at[v];
+        my_rank += (other < mine || (other == mine && v < w)) ? 1 : 0;
+      }
+      by_rank[my_rank] = w;
+    }
+    __syncthreads();
+    for (int l = threadIdx.x; l < tiles_per_group; l += blockDim.x) {
+      const int round = l / workers, to = by_rank[l - round * workers];
+      sched[(long long)to * sched_stride + count[to] + round] = g * tiles_per_group + l;
+    }
+    __syncthreads();
+    if (w < workers) {
+      const int got = full + (my_rank < rest ? 1 : 0);
+      count[w] += got;
+      free_at[w] += (long long)got * max(KG_MIN_COST, __ldg(&kseg[g]).y);
+    }
+    __syncthreads();
+  }
+  if (w < workers) sched_count[w] = count[w];
+}
+
 // x [k_total, cols] (16-bit elements, row stride ldx) -> xt [k blocks, cols, 64].  Block (bx, by) produces K block bx
 // of rows [64 by, 64 by + 64), 8 KB of contiguous output: one 64 x 64 tile through shared memory, 32-bit accesses
 // both ways.
@@ -496,7 +574,8 @@ transpose_align_kernel(const uint16_t* __restrict__ x, long long ldx, int cols, 
 static int run_gemm16(const void* a, int64_t a_map_rows, const void* b, int64_t b_map_rows, int dtype, int64_t m,
                       int64_t n, int64_t k, const int2* kseg, int b_group_rows, long long c_group_rows,
                       const int32_t* tiles, int max_tiles, int tile_rows, void* c, int64_t ldc, int32_t* status,
-                      void* stream) {
+                      void* stream, const int* sched = nullptr, const int* sched_count = nullptr,
+                      int sched_stride = 0) {
   int rc = check_device();
   if (rc != DLB_OK) return rc;
   CUtensorMap ma, mb;
@@ -510,6 +589,10 @@ static int run_gemm16(const void* a, int64_t a_map_rows, const void* b, int64_t 
   g.n = (int)n;
   g.k_bytes = (int)(2 * k);
   g.kseg = kseg;
+  g.group_m_tiles = (int)ceil_div(m, (int64_t)tile_rows);
+  g.sched = sched;
+  g.sched_count = sched_count;
+  g.sched_stride = sched_stride;
   g.b_group_rows = b_group_rows;
   g.c_group_rows = c_group_rows;
   const int ctas = tile_rows / BM;
@@ -566,7 +649,11 @@ extern "C" int64_t dlb_k_grouped_gemm_workspace_bytes(int64_t k_total, int64_t m
   if (k_total < 0 || m <= 0 || n <= 0 || num_groups <= 0 || (tile_rows != 128 && tile_rows != 256)) return -1;
   const int64_t kal = k_grouped_kal(k_total, num_groups);
   const int64_t m_tiles = ceil_div(m, (int64_t)tile_rows);
-  return 2 * kal * (m + n) + 16 * (1 + num_groups * m_tiles) + 8 * (int64_t)num_groups + 16 * (int64_t)num_groups;
+  const int64_t per_group = m_tiles * ceil_div(n, (int64_t)BN);
+  // tile lists: at most per_group / workers + 1 tiles per group and worker; sized for any worker count up to 256
+  const int64_t sched_ints = 256 + num_groups * (per_group + 256);
+  return 2 * kal * (m + n) + 16 * (1 + num_groups * m_tiles) + 8 * (int64_t)num_groups + 16 * (int64_t)num_groups +
+         4 * sched_ints;
 }
 
 extern "C" int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t k_total, int64_t m, int64_t n,
@@ -602,10 +689,21 @@ extern "C" int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype,
   int4* tiles = reinterpret_cast<int4*>(w + 2 * kal * (m + n));
   KSpan* span = reinterpret_cast<KSpan*>(tiles + 1 + num_groups * m_tiles);
   int2* kseg = reinterpret_cast<int2*>(span + num_groups);
+  int* sched_count = reinterpret_cast<int*>(kseg + num_groups);
+  int* sched = sched_count + 256;
+  const int64_t per_group = m_tiles * ceil_div(n, (int64_t)BN);
+  const int64_t all_tiles = per_group * num_groups;
+  const int max_workers = sm_count() / (tile_rows / BM);
+  const int workers = (int)(all_tiles < max_workers ? all_tiles : max_workers);   // as run_gemm16 sizes its grid
+  DLB_REQUIRE(workers <= 256, DLB_ERR_INVALID, "k_grouped_gemm_16bit: more than 256 workers");
+  const int sched_stride = (int)(num_groups * (per_group / workers + 1));
   cudaStream_t st = (cudaStream_t)stream;
   k_group_plan_kernel<<<1, 256, 0, st>>>(reinterpret_cast<const long long*>(group_sizes), num_groups, k_total, (int)m,
                                          tile_rows, kseg, span, tiles);
   if ((rc = check_cuda(cudaGetLastError(), "k_group_plan_kernel")) != DLB_OK) return rc;
+  count_launch();
+  k_group_schedule_kernel<<<1, 256, 0, st>>>(kseg, num_groups, (int)per_group, workers, sched, sched_count, sched_stride);
+  if ((rc = check_cuda(cudaGetLastError(), "k_group_schedule_kernel")) != DLB_OK) return rc;
   count_launch();
   const dim3 ga((unsigned)(kal / 64), (unsigned)ceil_div(m, (int64_t)64)), gb((unsigned)(kal / 64), (unsigned)ceil_div(n, (int64_t)64));
   transpose_align_kernel<<<ga, 256, 0, st>>>(reinterpret_cast<const uint16_t*>(a), m, (int)m, kseg, span, num_groups, at);
@@ -615,5 +713,5 @@ extern "C" int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype,
   if ((rc = check_cuda(cudaGetLastError(), "transpose_align_kernel(b)")) != DLB_OK) return rc;
   count_launch();
   return run_gemm16(at, kal / 64 * m, bt, kal / 64 * n, dtype, m, n, 64, kseg, 0, m, reinterpret_cast<const int32_t*>(tiles),
-                    (int)(num_groups * m_tiles), tile_rows, c, n, status, stream);
+                    (int)(num_groups * m_tiles), tile_rows, c, n, status, stream, sched, sched_count, sched_stride);
 }
