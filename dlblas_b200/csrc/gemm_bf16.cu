@@ -31,7 +31,7 @@ template <int CTAS> struct Geo {
   static constexpr int STAGES = CTAS == 1 ? 3 : 4;
   static constexpr int STAGING_OFF = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFF = STAGING_OFF + BM * (BN * 2 + 16);
-  static constexpr int NUM_BARS = 2 * STAGES + 2 * 2 + 3;
+  static constexpr int NUM_BARS = 3 * STAGES + 2 * 2 + 3;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = MISC_OFF + 16 + 1024;
 };
@@ -51,14 +51,15 @@ struct Args16 {
   const int4* tiles;     // nullptr: one group, M tiles derived from m
   int m, n, k_bytes;
   int num_m_tiles_static, num_n_tiles;
-  // Groups along the reduction dimension (k_grouped_gemm): tile {g, row0, rows} multiplies rows [row0, row0 + rows) of
-  // A by rows [n0, ...) of B over the K blocks of group g, kseg[g] = {first K block, number of K blocks (>= 1)}, and
-  // writes rows g * c_group_rows + row0 ... of C.  Both operands are then stored K block by K block, A as
-  // [k blocks, m, 64] and B as [k blocks, n, 64], so a tile's K block is one contiguous run of 128-byte rows.
-  // Otherwise kseg is null, the operands are [rows, k], the K range is the whole K, B holds one [n, k] matrix per group
+  // Groups along the reduction dimension (k_grouped_gemm): the operands are A [k_total, m] and B [k_total, n], both
+  // MN-major (a row holds one k), tile {g, row0, rows} multiplies columns [row0, row0 + rows) of A by columns
+  // [n0, ...) of B over the K rows of group g, kseg[g] = {first K row, number of 64-row K blocks (>= 1), valid rows of
+  // the last block (0 ... 64), 0}, and writes rows g * c_group_rows + row0 ... of C.  Otherwise kseg is null, the
+  // operands are [rows, k] K-major, the K range is the whole K, B holds one [n, k] matrix per group
   // (b_group_rows = n) and c_group_rows = 0.
-  const int2* kseg;
+  const int4* kseg;
   int group_m_tiles;   // m tiles per group when kseg is given
+  int band;            // n tiles per band of the tile order when kseg is given
   // Per-worker tile lists (a worker is a CTA or a pair): worker w runs tiles sched[w * sched_stride + i] for
   // i < sched_count[w].  Null: worker w runs tiles w, w + workers, ...
   const int* sched;
@@ -96,27 +97,51 @@ __device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+// Shared-memory descriptor of an MN-major operand tile with 128-byte swizzle: rows of 128 bytes hold 64 consecutive
+// M (or N) elements of one k; 64 such rows (8 KB) per block of 64 columns, the blocks 8 KB apart (leading byte offset),
+// groups of 8 k rows 1 KB apart (stride byte offset).
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);
+  d |= (uint64_t)(8192 >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Zeroes K rows [valid, 64) of every 64-column block of a stage (whole 128-byte rows, so the swizzle inside a row does
+// not matter) and orders the writes before the tensor core's reads.  Called by one whole warp.
+__device__ __forceinline__ void clear_k_rows(uint8_t* stage, int blocks, int valid, int lane) {
+  const int units = (64 - valid) * 8;
+  for (int c = 0; c < blocks; ++c) {
+    uint4* p = reinterpret_cast<uint4*>(stage + c * 8192 + valid * 128);
+    for (int u = lane; u < units; u += 32) p[u] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 struct Tile16 {
   int e, row0, rows, n0;
 };
-constexpr int KG_BAND = 8;   // n tiles per band in the tile order of k-grouped launches
+constexpr int KG_BAND = 4;   // default n tiles per band in the tile order of k-grouped launches
 
 template <int CTAS> __device__ __forceinline__ Tile16 decode16(const Args16& g, int t) {
   Tile16 ti;
   int m_tile = t / g.num_n_tiles;
   int n_tile = t - m_tile * g.num_n_tiles;
   if (g.kseg != nullptr) {
-    // Every group has the same m x n grid of tiles.  Walk it in bands of KG_BAND n tiles, m tile by m tile inside a
-    // band: the tiles in flight at one time (one per CTA or pair) then cover about as many A row blocks as B row
-    // blocks, and a band of B stays in L2 while A streams past it (measured with ragged K ranges of up to 10 k:
-    // DRAM reads 12.2 -> see the profile of this kernel).
+    // Every group has the same m x n grid of tiles.  Walk it in bands of `band` n tiles, m tile by m tile inside a
+    // band, so that the tiles in flight at one time share rows of both operands and a band of B can stay in L2 while
+    // A streams past it.  Measured on 128 ragged groups (K 0 ... 10 k): bands of 3 to 8 are within 3 % of one another
+    // and up to 10 % faster than whole rows of n tiles; DLBLAS_KGROUP_BAND overrides the default.
     const int per_group = g.group_m_tiles * g.num_n_tiles;
     const int grp = t / per_group, l = t - grp * per_group;
-    const int band = l / (g.group_m_tiles * KG_BAND), li = l - band * g.group_m_tiles * KG_BAND;
-    const int width = min(KG_BAND, g.num_n_tiles - band * KG_BAND);
+    const int band = l / (g.group_m_tiles * g.band), li = l - band * g.group_m_tiles * g.band;
+    const int width = min(g.band, g.num_n_tiles - band * g.band);
     const int mt = li / width;
     m_tile = grp * g.group_m_tiles + mt;
-    n_tile = band * KG_BAND + (li - mt * width);
+    n_tile = band * g.band + (li - mt * width);
   }
   if (g.tiles != nullptr) {
     const int4 v = __ldg(g.tiles + 1 + m_tile);
@@ -160,6 +185,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 2 * TMEM_BUFS);
   const uint32_t staged_bar = drain_bar + 8u;
   const uint32_t sfree_bar = drain_bar + 16u;
+  auto land_bar = [&](int s) { return drain_bar + 24u + 8u * s; };   // k-grouped launches: this CTA's loads of a stage
   uint8_t* staging = smem + G::STAGING_OFF;
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + G::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::MISC_OFF + 4);
@@ -182,6 +208,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
+      mbar_init(land_bar(s), 1);
     }
     for (int b = 0; b < TMEM_BUFS; ++b) {
       mbar_init(tfull_bar(b), 1);
@@ -222,19 +249,58 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     for (int i = 0; i < my_tiles && ok; ++i) {
       const int t = tile_at(i);
       const Tile16 ti = decode16<CTAS>(g, t);
-      const int2 ks = g.kseg != nullptr ? __ldg(g.kseg + ti.e) : make_int2(0, kblocks);
-      const bool blocked = g.kseg != nullptr;
+      const bool mn = g.kseg != nullptr;
+      const int4 ks = mn ? __ldg(g.kseg + ti.e) : make_int4(0, kblocks, 64, 0);
       for (int kb = 0; kb < ks.y; ++kb, ++it) {
         const int s = it % STAGES;
-        const int kx = blocked ? 0 : kb * UMMA_BK_BYTES;
-        const int a_row = ti.row0 + (blocked ? (ks.x + kb) * g.m : 0);
-        const int b_row = ti.n0 + (blocked ? (ks.x + kb) * g.n : ti.e * g.b_group_rows);
         if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, abort_flag, limit)) {
           ok = false;
           break;
         }
         const uint32_t a_dst = smem_base + s * STAGE_BYTES;
         const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+        if (mn) {
+          // MN-major operands: boxes of 64 K rows x 128 bytes (64 columns), one per 64 columns of the tile.  A block
+          // that ends inside its box (rows of the next group follow) lands on this CTA's own barrier; the MMA warp
+          // clears those rows before the block is used.  Every other block goes the usual way, and the own barrier
+          // is stepped by hand so that its phase follows the stage's.
+          const bool ragged = kb == ks.y - 1 && ks.z < 64;
+          const int ky = ks.x + kb * 64;
+          const int ax = 2 * (ti.row0 + (int)rank * BM), bx = 2 * (ti.n0 + (int)rank * (BN / CTAS));
+          if (elect_one()) {
+            if (ragged) {
+              mbar_expect_tx(land_bar(s), STAGE_BYTES);
+#pragma unroll
+              for (int c = 0; c < BM / 64; ++c) tma_load_2d(a_dst + c * 8192, &tmap_a, ax + 128 * c, ky, land_bar(s));
+#pragma unroll
+              for (int c = 0; c < BN / CTAS / 64; ++c)
+                tma_load_2d(b_dst + c * 8192, &tmap_b, bx + 128 * c, ky, land_bar(s));
+            } else {
+              mbar_arrive(land_bar(s));
+              if constexpr (PAIR) {
+                const uint32_t lead_full = mapa(full_bar(s), 0);
+                if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+#pragma unroll
+                for (int c = 0; c < BM / 64; ++c)
+                  tma_load_2d_pair(a_dst + c * 8192, &tmap_a, ax + 128 * c, ky, lead_full);
+#pragma unroll
+                for (int c = 0; c < BN / CTAS / 64; ++c)
+                  tma_load_2d_pair(b_dst + c * 8192, &tmap_b, bx + 128 * c, ky, lead_full);
+              } else {
+                mbar_expect_tx(full_bar(s), STAGE_BYTES);
+#pragma unroll
+                for (int c = 0; c < BM / 64; ++c) tma_load_2d(a_dst + c * 8192, &tmap_a, ax + 128 * c, ky, full_bar(s));
+#pragma unroll
+                for (int c = 0; c < BN / 64; ++c) tma_load_2d(b_dst + c * 8192, &tmap_b, bx + 128 * c, ky, full_bar(s));
+              }
+            }
+          }
+          __syncwarp();
+          continue;
+        }
+        const int kx = kb * UMMA_BK_BYTES;
+        const int a_row = ti.row0;
+        const int b_row = ti.n0 + ti.e * g.b_group_rows;
         if constexpr (PAIR) {
           const uint32_t lead_full = mapa(full_bar(s), 0);
           if (elect_one()) {
@@ -259,6 +325,27 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   } else if (warp == MMA_WARP) {
     uint32_t it = 0, tile_no = 0;
     bool ok = true;
+    const bool mn = g.kseg != nullptr;
+    // The other CTA of a pair issues nothing.  With MN-major operands it still clears the rows past the end of each
+    // tile's last K block in its own shared memory and then completes the leader's barrier of that stage.  It follows
+    // every use of every stage's barrier, block by block: a parity wait only tells the current phase from the one
+    // before it, so a waiter that skipped uses could take an earlier phase for the one it wants.
+    for (int i = 0; PAIR && mn && rank != 0 && i < my_tiles && ok; ++i) {
+      const int4 ks = __ldg(g.kseg + decode16<CTAS>(g, tile_at(i)).e);
+      for (int kb = 0; kb < ks.y; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(land_bar(s), (it / STAGES) & 1u, abort_flag, limit)) {
+          ok = false;
+          break;
+        }
+        if (kb == ks.y - 1 && ks.z < 64) {
+          clear_k_rows(smem + s * STAGE_BYTES, STAGE_BYTES / 8192, ks.z, lane);
+          __syncwarp();
+          if (elect_one()) mbar_arrive_cluster(mapa(full_bar(s), 0));
+          __syncwarp();
+        }
+      }
+    }
     for (int i = 0; i < my_tiles && ok && rank == 0; ++i, ++tile_no) {
       const int t = tile_at(i);
       const int b = tile_no % TMEM_BUFS;
@@ -267,28 +354,42 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         break;
       }
       const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-      const int nkb = g.kseg != nullptr ? __ldg(g.kseg + decode16<CTAS>(g, t).e).y : kblocks;
+      const int4 ks = mn ? __ldg(g.kseg + decode16<CTAS>(g, t).e) : make_int4(0, kblocks, 64, 0);
+      const int nkb = ks.y;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = it % STAGES;
+        if (mn && kb == nkb - 1 && ks.z < 64) {
+          if (!mbar_wait(land_bar(s), (it / STAGES) & 1u, abort_flag, limit)) {
+            ok = false;
+            break;
+          }
+          clear_k_rows(smem + s * STAGE_BYTES, STAGE_BYTES / 8192, ks.z, lane);
+          __syncwarp();
+          if constexpr (!PAIR) {
+            if (elect_one()) mbar_arrive(full_bar(s));   // nothing else completes this stage's barrier
+            __syncwarp();
+          }
+        }
         if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, abort_flag, limit)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t a_addr = smem_base + s * STAGE_BYTES;
-        const uint64_t a_desc = make_smem_desc(a_addr);
-        const uint64_t b_desc = make_smem_desc(a_addr + A_STAGE_BYTES);
+        const uint64_t a_desc = mn ? make_smem_desc_mn(a_addr) : make_smem_desc(a_addr);
+        const uint64_t b_desc = mn ? make_smem_desc_mn(a_addr + A_STAGE_BYTES) : make_smem_desc(a_addr + A_STAGE_BYTES);
+        const uint32_t kstep = mn ? (2048u >> 4) : 2u;   // 16 K: two 8-row swizzle atoms / 32 bytes along the row
         if (elect_one()) {
           if constexpr (PAIR) {
 #pragma unroll
             for (int kk = 0; kk < UMMA_BK_BYTES / 32; ++kk)
-              tc_mma_f16_pair(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              tc_mma_f16_pair(d_tmem, a_desc + kstep * kk, b_desc + kstep * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             tc_commit_pair(empty_bar(s));                          // frees the stage in both CTAs
             if (kb == nkb - 1) tc_commit_pair(tfull_bar(b));       // both CTAs' drain warps
           } else {
 #pragma unroll
             for (int kk = 0; kk < UMMA_BK_BYTES / 32; ++kk)
-              tc_mma_f16(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              tc_mma_f16(d_tmem, a_desc + kstep * kk, b_desc + kstep * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             tc_commit(empty_bar(s));
             if (kb == nkb - 1) tc_commit(tfull_bar(b));
           }
@@ -296,7 +397,7 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         __syncwarp();
       }
     }
-    if (!ok) {
+    if (!ok && rank == 0) {
       if (elect_one()) {
         if constexpr (PAIR)
           asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(drain_bar)
@@ -322,8 +423,8 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       const int my_row0 = ti.row0 + (int)rank * BM;               // this CTA's 128 rows of the tile
       const int my_rows = min(BM, max(0, ti.rows - (int)rank * BM));
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int row = ew * 64 + i * 32 + lane;
+      for (int h = 0; h < 2; ++h) {
+        const int row = ew * 64 + h * 32 + lane;
         if (row < my_rows)
           bulk_store(reinterpret_cast<T*>(g.c) + ((long long)my_row0 + row + ti.e * g.c_group_rows) * g.ldc + ti.n0,
                      smem_u32(staging + row * STAGING_ROW_BYTES), bytes);
@@ -444,32 +545,23 @@ int launch16(const CUtensorMap& ma, const CUtensorMap& mb, const Args16& g, int 
 
 // ---- groups along the reduction dimension (k_grouped_gemm) ----------------------------------------------------------
 // C[g] = A_g^T B_g with A [k_total, m], B [k_total, n] row-major and group g owning rows [start_g, start_g + size_g).
-// The tensor cores want both operands K-major, so each operand is transposed once into K blocks of 64 elements,
-// [k blocks, m or n, 64]: every group's K range starts on a block boundary and is zero-filled up to the next one, and
-// an empty group gets one block of zeros so that its tiles still run and write zeros.  One K block of a tile is then
-// 128 or 256 consecutive 128-byte rows (a [m, k] layout with rows megabytes apart measured 40 % slower at
-// k_total = 650 k: every row of a TMA box on its own page).
-
-struct KSpan {
-  long long start;   // first row of the group in A and B
-  long long size;    // its rows, clipped to what k_total leaves
-};
+// Both operands are MN-major for the tensor cores (a row of memory holds one k), which tcgen05.mma takes as they are:
+// nothing is transposed or copied.  TMA places no alignment rule on the outer (K) coordinate, so a group may start at
+// any row; its last 64-row block may run into the next group's rows, which the MMA warp clears in shared memory.  An
+// empty group gets one block with no valid row so that its tiles still run and write zeros.
 
 // One block.  Thread 0 scans the group sizes; all threads then write the tile list {group, row0, rows}.
 __global__ void k_group_plan_kernel(const long long* __restrict__ sizes, int groups, long long k_total, int m,
-                                    int tile_rows, int2* __restrict__ kseg, KSpan* __restrict__ span,
-                                    int4* __restrict__ tiles) {
+                                    int tile_rows, int4* __restrict__ kseg, int4* __restrict__ tiles) {
   if (threadIdx.x == 0) {
-    long long run = 0, kal = 0;
+    long long run = 0;
     for (int g = 0; g < groups; ++g) {
       long long sz = sizes[g];
       sz = sz < 0 ? 0 : sz;
       sz = sz > k_total - run ? k_total - run : sz;
       const long long nkb = sz == 0 ? 1 : (sz + 63) / 64;
-      span[g] = KSpan{run, sz};
-      kseg[g] = make_int2((int)kal, (int)nkb);
+      kseg[g] = make_int4((int)run, (int)nkb, (int)(sz - 64 * (nkb - 1)), 0);
       run += sz;
-      kal += nkb;
     }
   }
   const int m_tiles = (m + tile_rows - 1) / tile_rows;
@@ -491,7 +583,7 @@ __global__ void k_group_plan_kernel(const long long* __restrict__ sizes, int gro
 constexpr int KG_MIN_COST = 8;
 
 __global__ void __launch_bounds__(256)
-k_group_schedule_kernel(const int2* __restrict__ kseg, int groups, int tiles_per_group, int workers,
+k_group_schedule_kernel(const int4* __restrict__ kseg, int groups, int tiles_per_group, int workers,
                         int* __restrict__ sched, int* __restrict__ sched_count, int sched_stride) {
   __shared__ long long free_at[256];
   __shared__ int count[256];
@@ -529,58 +621,18 @@ k_group_schedule_kernel(const int2* __restrict__ kseg, int groups, int tiles_per
   if (w < workers) sched_count[w] = count[w];
 }
 
-// x [k_total, cols] (16-bit elements, row stride ldx) -> xt [k blocks, cols, 64].  Block (bx, by) produces K block bx
-// of rows [64 by, 64 by + 64), 8 KB of contiguous output: one 64 x 64 tile through shared memory, 32-bit accesses
-// both ways.
-__global__ void __launch_bounds__(256)
-transpose_align_kernel(const uint16_t* __restrict__ x, long long ldx, int cols, const int2* __restrict__ kseg,
-                       const KSpan* __restrict__ span, int groups, uint16_t* __restrict__ xt) {
-  __shared__ uint32_t tile[64][33];
-  const int blk = blockIdx.x;
-  int lo = 0, hi = groups - 1;                      // the last group that starts at or before this K block
-  while (lo < hi) {
-    const int mid = (lo + hi + 1) >> 1;
-    if (__ldg(&kseg[mid]).x <= blk) lo = mid; else hi = mid - 1;
-  }
-  const int2 ks = __ldg(&kseg[lo]);
-  if (blk - ks.x >= ks.y) return;                   // past the last group's blocks: nothing reads there
-  const long long k0 = 64ll * (blk - ks.x);
-  const KSpan sp = span[lo];
-  const int valid = (int)max(0ll, min(64ll, sp.size - k0));
-  const int m0 = 64 * blockIdx.y;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int kl = ty + 8 * i;
-    uint32_t v = 0;
-    if (kl < valid && m0 + 2 * tx < cols)
-      v = *reinterpret_cast<const uint32_t*>(x + (sp.start + k0 + kl) * ldx + m0 + 2 * tx);
-    tile[kl][tx] = v;
-  }
-  __syncthreads();
-  const uint16_t* t16 = reinterpret_cast<const uint16_t*>(&tile[0][0]);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int ml = ty + 8 * i;
-    if (m0 + ml < cols) {
-      const uint32_t a = t16[(2 * tx) * 66 + ml], b = t16[(2 * tx + 1) * 66 + ml];
-      *reinterpret_cast<uint32_t*>(xt + ((long long)blk * cols + m0 + ml) * 64 + 2 * tx) = a | (b << 16);
-    }
-  }
-}
-
-// Maps, arguments and launch shared by the two entry points.  a: [a_map_rows, k] and b: [b_map_rows, k] 16-bit,
-// K-major, as the tensor maps see them; m rows of A (per K block when kseg is given) meet n rows of B.
-static int run_gemm16(const void* a, int64_t a_map_rows, const void* b, int64_t b_map_rows, int dtype, int64_t m,
-                      int64_t n, int64_t k, const int2* kseg, int b_group_rows, long long c_group_rows,
-                      const int32_t* tiles, int max_tiles, int tile_rows, void* c, int64_t ldc, int32_t* status,
-                      void* stream, const int* sched = nullptr, const int* sched_count = nullptr,
-                      int sched_stride = 0) {
+// Maps, arguments and launch shared by the two entry points.  The tensor maps see a as [a_map_rows, a_row_bytes] and b
+// as [b_map_rows, b_row_bytes] with boxes of box_rows rows; m rows (columns when kseg is given) of A meet n of B.
+static int run_gemm16(const void* a, int64_t a_map_rows, int64_t a_row_bytes, const void* b, int64_t b_map_rows,
+                      int64_t b_row_bytes, int box_rows, int dtype, int64_t m, int64_t n, int64_t k, const int4* kseg,
+                      int b_group_rows, long long c_group_rows, const int32_t* tiles, int max_tiles, int tile_rows,
+                      void* c, int64_t ldc, int32_t* status, void* stream, const int* sched = nullptr,
+                      const int* sched_count = nullptr, int sched_stride = 0) {
   int rc = check_device();
   if (rc != DLB_OK) return rc;
   CUtensorMap ma, mb;
-  if ((rc = make_map(&ma, a, (uint64_t)a_map_rows, (uint64_t)(2 * k))) != DLB_OK) return rc;
-  if ((rc = make_map(&mb, b, (uint64_t)b_map_rows, (uint64_t)(2 * k))) != DLB_OK) return rc;
+  if ((rc = make_map_box(&ma, a, (uint64_t)a_map_rows, (uint64_t)a_row_bytes, (uint32_t)box_rows)) != DLB_OK) return rc;
+  if ((rc = make_map_box(&mb, b, (uint64_t)b_map_rows, (uint64_t)b_row_bytes, (uint32_t)box_rows)) != DLB_OK) return rc;
   Args16 g = {};
   g.c = c;
   g.ldc = ldc;
@@ -590,6 +642,8 @@ static int run_gemm16(const void* a, int64_t a_map_rows, const void* b, int64_t 
   g.k_bytes = (int)(2 * k);
   g.kseg = kseg;
   g.group_m_tiles = (int)ceil_div(m, (int64_t)tile_rows);
+  const char* band_env = getenv("DLBLAS_KGROUP_BAND");
+  g.band = band_env != nullptr && atoi(band_env) > 0 ? atoi(band_env) : KG_BAND;
   g.sched = sched;
   g.sched_count = sched_count;
   g.sched_stride = sched_stride;
@@ -599,6 +653,7 @@ static int run_gemm16(const void* a, int64_t a_map_rows, const void* b, int64_t 
   g.num_m_tiles_static = (int)ceil_div(m, (int64_t)tile_rows);
   g.num_n_tiles = (int)ceil_div(n, (int64_t)BN);
   g.idesc = make_idesc16(dtype == DLB_BF16 ? 1u : 0u, ctas);
+  if (kseg != nullptr) g.idesc |= (1u << 15) | (1u << 16);   // A and B MN-major
   g.status = status;
   g.timeout_cycles = wait_limit_cycles(DEFAULT_TIMEOUT_CYCLES);
   const int workers = sm_count() / ctas;
@@ -637,23 +692,19 @@ extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, i
   DLB_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 16 == 0) &&
                   ((uintptr_t)tiles % 16 == 0),
               DLB_ERR_INVALID, "grouped_gemm_16bit: a, b, c and tiles must be 16-byte aligned");
-  return run_gemm16(a, rows, b, (int64_t)num_groups * n, dtype, rows, n, k, nullptr, (int)n, 0, tiles, max_tiles,
-                    tile_rows, c, ldc, status, stream);
+  return run_gemm16(a, rows, 2 * k, b, (int64_t)num_groups * n, 2 * k, 128, dtype, rows, n, k, nullptr, (int)n, 0, tiles,
+                    max_tiles, tile_rows, c, ldc, status, stream);
 }
 
-// Workspace of dlb_k_grouped_gemm_16bit, in bytes: both transposed operands, the K ranges and the tile list.
-static int64_t k_grouped_kal(int64_t k_total, int num_groups) { return (k_total + 63) / 64 * 64 + 64ll * num_groups; }
-
+// Workspace of dlb_k_grouped_gemm_16bit, in bytes: the tile list, the K ranges and the workers' tile lists.
 extern "C" int64_t dlb_k_grouped_gemm_workspace_bytes(int64_t k_total, int64_t m, int64_t n, int num_groups,
                                                       int tile_rows) {
   if (k_total < 0 || m <= 0 || n <= 0 || num_groups <= 0 || (tile_rows != 128 && tile_rows != 256)) return -1;
-  const int64_t kal = k_grouped_kal(k_total, num_groups);
   const int64_t m_tiles = ceil_div(m, (int64_t)tile_rows);
   const int64_t per_group = m_tiles * ceil_div(n, (int64_t)BN);
   // tile lists: at most per_group / workers + 1 tiles per group and worker; sized for any worker count up to 256
   const int64_t sched_ints = 256 + num_groups * (per_group + 256);
-  return 2 * kal * (m + n) + 16 * (1 + num_groups * m_tiles) + 8 * (int64_t)num_groups + 16 * (int64_t)num_groups +
-         4 * sched_ints;
+  return 16 * (1 + num_groups * m_tiles) + 16 * (int64_t)num_groups + 4 * sched_ints;
 }
 
 extern "C" int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t k_total, int64_t m, int64_t n,
@@ -666,9 +717,10 @@ extern "C" int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype,
   DLB_REQUIRE(m % 8 == 0 && n % 8 == 0, DLB_ERR_INVALID,
               "k_grouped_gemm_16bit: m=%lld and n=%lld must be multiples of 8 (16-byte rows)", (long long)m, (long long)n);
   DLB_REQUIRE(tile_rows == 128 || tile_rows == 256, DLB_ERR_INVALID, "k_grouped_gemm_16bit: tile_rows must be 128 or 256");
-  const int64_t kal = k_grouped_kal(k_total, num_groups);
   const int64_t m_tiles = ceil_div(m, (int64_t)tile_rows);
-  DLB_REQUIRE(kal / 64 * m < (1ll << 31) && kal / 64 * n < (1ll << 31) && num_groups * m_tiles < (1ll << 24),
+  const int64_t per_group = m_tiles * ceil_div(n, (int64_t)BN);
+  const int64_t all_tiles = per_group * num_groups;
+  DLB_REQUIRE(k_total < (1ll << 31) - 64 && 2 * m < (1ll << 31) && 2 * n < (1ll << 31) && all_tiles < (1ll << 30),
               DLB_ERR_INVALID, "k_grouped_gemm_16bit: size too large");
   if (k_total == 0) {   // nothing to reduce over: every group is empty
     DLB_REQUIRE(c != nullptr, DLB_ERR_INVALID, "k_grouped_gemm_16bit: null pointer");
@@ -676,42 +728,30 @@ extern "C" int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype,
                       "cudaMemsetAsync(k_grouped_gemm_16bit, c)");
   }
   DLB_REQUIRE(a && b && c && group_sizes && workspace, DLB_ERR_INVALID, "k_grouped_gemm_16bit: null pointer");
-  DLB_REQUIRE(((uintptr_t)a % 4 == 0) && ((uintptr_t)b % 4 == 0) && ((uintptr_t)c % 16 == 0) &&
-                  ((uintptr_t)workspace % 128 == 0),
-              DLB_ERR_INVALID, "k_grouped_gemm_16bit: a, b must be 4-byte, c 16-byte and workspace 128-byte aligned");
+  DLB_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 16 == 0) &&
+                  ((uintptr_t)workspace % 16 == 0),
+              DLB_ERR_INVALID, "k_grouped_gemm_16bit: a, b, c and workspace must be 16-byte aligned");
   DLB_REQUIRE(workspace_bytes >= dlb_k_grouped_gemm_workspace_bytes(k_total, m, n, num_groups, tile_rows), DLB_ERR_INVALID,
               "k_grouped_gemm_16bit: workspace of %lld bytes is too small", (long long)workspace_bytes);
   int rc = check_device();
   if (rc != DLB_OK) return rc;
-  uint8_t* w = reinterpret_cast<uint8_t*>(workspace);
-  uint16_t* at = reinterpret_cast<uint16_t*>(w);
-  uint16_t* bt = reinterpret_cast<uint16_t*>(w + 2 * kal * m);
-  int4* tiles = reinterpret_cast<int4*>(w + 2 * kal * (m + n));
-  KSpan* span = reinterpret_cast<KSpan*>(tiles + 1 + num_groups * m_tiles);
-  int2* kseg = reinterpret_cast<int2*>(span + num_groups);
+  int4* tiles = reinterpret_cast<int4*>(workspace);
+  int4* kseg = tiles + 1 + num_groups * m_tiles;
   int* sched_count = reinterpret_cast<int*>(kseg + num_groups);
   int* sched = sched_count + 256;
-  const int64_t per_group = m_tiles * ceil_div(n, (int64_t)BN);
-  const int64_t all_tiles = per_group * num_groups;
   const int max_workers = sm_count() / (tile_rows / BM);
   const int workers = (int)(all_tiles < max_workers ? all_tiles : max_workers);   // as run_gemm16 sizes its grid
   DLB_REQUIRE(workers <= 256, DLB_ERR_INVALID, "k_grouped_gemm_16bit: more than 256 workers");
   const int sched_stride = (int)(num_groups * (per_group / workers + 1));
   cudaStream_t st = (cudaStream_t)stream;
   k_group_plan_kernel<<<1, 256, 0, st>>>(reinterpret_cast<const long long*>(group_sizes), num_groups, k_total, (int)m,
-                                         tile_rows, kseg, span, tiles);
+                                         tile_rows, kseg, tiles);
   if ((rc = check_cuda(cudaGetLastError(), "k_group_plan_kernel")) != DLB_OK) return rc;
   count_launch();
   k_group_schedule_kernel<<<1, 256, 0, st>>>(kseg, num_groups, (int)per_group, workers, sched, sched_count, sched_stride);
   if ((rc = check_cuda(cudaGetLastError(), "k_group_schedule_kernel")) != DLB_OK) return rc;
   count_launch();
-  const dim3 ga((unsigned)(kal / 64), (unsigned)ceil_div(m, (int64_t)64)), gb((unsigned)(kal / 64), (unsigned)ceil_div(n, (int64_t)64));
-  transpose_align_kernel<<<ga, 256, 0, st>>>(reinterpret_cast<const uint16_t*>(a), m, (int)m, kseg, span, num_groups, at);
-  if ((rc = check_cuda(cudaGetLastError(), "transpose_align_kernel(a)")) != DLB_OK) return rc;
-  count_launch();
-  transpose_align_kernel<<<gb, 256, 0, st>>>(reinterpret_cast<const uint16_t*>(b), n, (int)n, kseg, span, num_groups, bt);
-  if ((rc = check_cuda(cudaGetLastError(), "transpose_align_kernel(b)")) != DLB_OK) return rc;
-  count_launch();
-  return run_gemm16(at, kal / 64 * m, bt, kal / 64 * n, dtype, m, n, 64, kseg, 0, m, reinterpret_cast<const int32_t*>(tiles),
-                    (int)(num_groups * m_tiles), tile_rows, c, n, status, stream, sched, sched_count, sched_stride);
+  return run_gemm16(a, k_total, 2 * m, b, k_total, 2 * n, 64, dtype, m, n, 64, kseg, 0, m,
+                    reinterpret_cast<const int32_t*>(tiles), (int)(num_groups * m_tiles), tile_rows, c, n, status, stream,
+                    sched, sched_count, sched_stride);
 }

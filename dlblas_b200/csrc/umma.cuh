@@ -231,19 +231,24 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D map over a row-major [rows, k] e4m3 matrix, box = 128 rows x 128 bytes, 128 B swizzle.
-int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k) {
+// 2-D map over a row-major [rows, k] byte matrix, box = box_rows rows x 128 bytes, 128 B swizzle.
+int make_map_box(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return fail(DLB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t gdim[2] = {k, rows};
   const cuuint64_t gstride[1] = {k};
-  const cuuint32_t box[2] = {UMMA_BK_BYTES, 128};
+  const cuuint32_t box[2] = {UMMA_BK_BYTES, box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(DLB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return DLB_OK;
+}
+
+// The operand tiles of the K-major kernels: 128 rows x 128 bytes.
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k) {
+  return make_map_box(map, base, rows, k, 128);
 }
 
 int check_device() {

@@ -3,9 +3,9 @@ C[g] = A[rows of g]^T @ B[rows of g] for contiguous row groups of sizes `size_pe
 (reduction) dimension; A [K, M], B [K, N], C [G, M, N] in the operands' 16-bit type, fp32 accumulation.  This is the
 weight-gradient GEMM of a grouped linear layer.
 
-The tcgen05 kernel reads both operands K-major, so each call transposes A and B once into a workspace whose groups
-start on 128-byte K-block boundaries (zero-filled tails; an empty group yields a zero C[g]).  The group offsets, the
-tile list and the transposition all run on the device; nothing synchronises with the host."""
+The tcgen05 kernel reads A and B where they lie, as MN-major operands (a row of memory holds one k): nothing is
+transposed or copied.  Group offsets, the tile list and the order in which the CTAs take the tiles are built on the
+device in a small workspace; nothing synchronises with the host.  An empty group yields a zero C[g]."""
 import os
 
 import torch

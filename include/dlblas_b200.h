@@ -273,11 +273,11 @@ DLB_API int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, int6
 /* k_grouped_gemm (dlblas/kernels/grouped_gemm/BF16/k_grouped_gemm.py:126-176, :254-330): groups along the reduction
  * dimension.  a [k_total, m] and b [k_total, n] row-major bf16 or fp16; group g owns the next group_sizes[g] rows of
  * both (int64 on the device; the sizes are clipped to k_total); c [num_groups, m, n] of the same type with
- * c[g] = a_g^T b_g, fp32 accumulation, zeros for an empty group.  m and n multiples of 8.  The call transposes both
- * operands into `workspace` (dlb_k_grouped_gemm_workspace_bytes bytes, 128-byte aligned, device memory) as blocks of
- * 64 K elements, every group's K range padded with zeros to whole blocks, and runs the tcgen05 kernel over
- * [group, m tile, n tile];
- * tile_rows as for dlb_grouped_gemm_16bit.  Nothing synchronises with the host. */
+ * c[g] = a_g^T b_g, fp32 accumulation, zeros for an empty group.  m and n multiples of 8.  The tensor cores read both
+ * operands where they lie (MN-major tcgen05 descriptors): nothing is transposed or copied.  `workspace`
+ * (dlb_k_grouped_gemm_workspace_bytes bytes, 16-byte aligned, device memory) holds the K ranges, the tile list over
+ * [group, m tile, n tile] and the per-CTA tile order, all built on the device; tile_rows as for
+ * dlb_grouped_gemm_16bit.  Nothing synchronises with the host. */
 DLB_API int64_t dlb_k_grouped_gemm_workspace_bytes(int64_t k_total, int64_t m, int64_t n, int num_groups, int tile_rows);
 DLB_API int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t k_total, int64_t m, int64_t n,
                              const int64_t* group_sizes, int num_groups, int tile_rows, void* workspace,
