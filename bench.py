@@ -592,6 +592,45 @@ def run_profile(args):
         torch.cuda.synchronize()
         _C.check_status(dev)
         return
+    if args.profile == "kgrouped":
+        # k_grouped_gemm at the shapes of the reference's benchmark (benchmarks/grouped_gemm/BF16/k_grouped_gemm.py:
+        # bf16, (m, n) in four pairs, random group sizes averaging 5120 rows): `experts` groups, CUDA events around
+        # whole calls, the torch loop of one matmul per group beside it.  `--steps 2` is the case for ncu.
+        import random
+        from dlblas_b200.kernels.grouped_gemm.BF16 import k_grouped_gemm
+        random.seed(0)
+        raw = [random.randint(0, 2 * 5120) for _ in range(e)]
+        sizes = torch.tensor(raw, dtype=torch.int64, device=dev)
+        k_total = sum(raw)
+        starts = [0]
+        for r in raw:
+            starts.append(starts[-1] + r)
+        shapes = ((3072, 4096),) if args.steps <= 2 else ((1536, 2048), (2048, 768), (3072, 4096), (4096, 1536))
+        print(f"| m | n | groups | K total | ms | TFLOP/s | of measured bf16 burst | torch per-group loop ms |\n|---|---|---|---|---|---|---|---|")
+        for (m, n) in shapes:
+            gd = torch.Generator(device=dev).manual_seed(7)
+            a = torch.randn(k_total, m, generator=gd, device=dev, dtype=torch.bfloat16)
+            b = torch.randn(k_total, n, generator=gd, device=dev, dtype=torch.bfloat16)
+            out = None
+            for _ in range(2):
+                out = k_grouped_gemm(a, b, sizes)
+            _C.check_status(dev)
+            if args.steps <= 2:
+                continue
+            ref = torch.empty_like(out)
+
+            def loop():
+                for i in range(e):
+                    torch.matmul(a[starts[i]:starts[i + 1]].t(), b[starts[i]:starts[i + 1]], out=ref[i])
+            ms = _time_kernel(lambda: k_grouped_gemm(a, b, sizes), dev, iters=args.steps)
+            ms_loop = _time_kernel(loop, dev, iters=max(3, args.steps // 4))
+            assert torch.equal(out, ref), "k_grouped_gemm differs from the per-group matmul"
+            tf = 2.0 * k_total * m * n / ms / 1e9
+            print(f"| {m} | {n} | {e} | {k_total} | {ms:.3f} | {tf:.0f} | {tf / load_peaks()['bf16_tflops']:.2f} | {ms_loop:.3f} |",
+                  flush=True)
+            del a, b, out, ref
+        torch.cuda.synchronize()
+        return
     w13, w13s, w2, w2s = make_weights(e, 1, dev)
     x = torch.randn(t, H, generator=g).to(torch.bfloat16).to(dev)
     ids = torch.stack([torch.randperm(e, generator=g)[:TOPK] for _ in range(t)]).to(dev)
@@ -841,7 +880,7 @@ def run_decode(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile", default="", choices=["", "gemm1", "gemm2", "dense", "gemm16", "bandwidth", "sweep"],
+    ap.add_argument("--profile", default="", choices=["", "gemm1", "gemm2", "dense", "gemm16", "kgrouped", "bandwidth", "sweep"],
                     help="run only one kernel on a small case (for ncu) and exit")
     ap.add_argument("--experts", type=int, default=32, help="experts of the --profile case")
     ap.add_argument("--gpus", type=int, default=1)

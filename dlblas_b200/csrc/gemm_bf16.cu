@@ -575,50 +575,76 @@ __global__ void k_group_plan_kernel(const long long* __restrict__ sizes, int gro
 // Tile lists for the workers of the GEMM (one block, at least `workers` threads).  Tiles are handed out in tile order,
 // group by group, each to the worker that a greedy scheduler would find free first, with a tile's cost taken as its
 // K blocks (at least KG_MIN_COST, the part of a tile that does not shrink with K).  All tiles of a group cost the same,
-// so inside a group the order of the workers by the time they become free does not change: one ranking per group, tile
-// l of the group to the worker of rank l mod workers.  Tiles that follow one another in tile order (and share rows of A
-// or B) thus start at about the same time whatever the K ranges of the groups before them; handing tile t to worker
-// t mod workers lets the workers drift apart by whole tiles once the groups differ in K, and the operands were then
-// read from DRAM 4.4 times instead of 1.5 (K ranges uniform in 0 ... 10 k).
+// so inside a group the order of the workers by the time they become free does not change: tile l of the group goes to
+// the worker of rank l mod workers, and the order is updated once per group.  Tiles that follow one another in tile
+// order (and share rows of A or B) thus start at about the same time whatever the K ranges of the groups before them;
+// handing tile t to worker t mod workers lets the workers drift apart by whole tiles once the groups differ in K, and
+// the operands were then read from DRAM 4.4 times instead of 2 (32 groups, K ranges uniform in 0 ... 10 k).
 constexpr int KG_MIN_COST = 8;
 
 __global__ void __launch_bounds__(256)
 k_group_schedule_kernel(const int4* __restrict__ kseg, int groups, int tiles_per_group, int workers,
                         int* __restrict__ sched, int* __restrict__ sched_count, int sched_stride) {
-  __shared__ long long free_at[256];
-  __shared__ int count[256];
-  __shared__ int by_rank[256];
-  const int w = threadIdx.x;
-  if (w < workers) {
-    free_at[w] = 0;
-    count[w] = 0;
+  // The workers in the order in which they become free, double-buffered: free_at[b][r] and who[b][r] for rank r.
+  __shared__ long long free_at[2][256];
+  __shared__ int who[2][256];
+  __shared__ int count[256];   // tiles given to each worker so far
+  __shared__ int cost_of[1024]; // the groups' tile costs, 1024 groups at a time (one global load per group would sit
+                                // on the critical path of the loop below)
+  const int r = threadIdx.x;
+  if (r < workers) {
+    free_at[0][r] = 0;
+    who[0][r] = r;
+    count[r] = 0;
   }
   __syncthreads();
   const int full = tiles_per_group / workers, rest = tiles_per_group - full * workers;
-  for (int g = 0; g < groups; ++g) {
-    int my_rank = 0;
-    if (w < workers) {
-      const long long mine = free_at[w];
-      for (int v = 0; v < workers; ++v) {
-        const long long other = free_at[v];
-        my_rank += (other < mine || (other == mine && v < w)) ? 1 : 0;
-      }
-      by_rank[my_rank] = w;
+  int cur = 0;
+  for (int g = 0; g < groups; ++g, cur ^= 1) {
+    if ((g & 1023) == 0) {
+      for (int j = threadIdx.x; j < min(1024, groups - g); j += blockDim.x)
+        cost_of[j] = max(KG_MIN_COST, __ldg(&kseg[g + j]).y);
+      __syncthreads();
     }
-    __syncthreads();
     for (int l = threadIdx.x; l < tiles_per_group; l += blockDim.x) {
-      const int round = l / workers, to = by_rank[l - round * workers];
+      const int round = l / workers, to = who[cur][l - round * workers];
       sched[(long long)to * sched_stride + count[to] + round] = g * tiles_per_group + l;
     }
-    __syncthreads();
-    if (w < workers) {
-      const int got = full + (my_rank < rest ? 1 : 0);
-      count[w] += got;
-      free_at[w] += (long long)got * max(KG_MIN_COST, __ldg(&kseg[g]).y);
+    // The first `rest` workers take one tile more than the others.  Both parts stay sorted, so the new order is a merge
+    // of the two: each worker finds its new rank with one binary search in the other part.
+    const long long cost = cost_of[g & 1023];
+    int new_rank = 0, me = 0, got = 0;
+    long long mine = 0;
+    if (r < workers) {
+      me = who[cur][r];
+      got = full + (r < rest ? 1 : 0);
+      mine = free_at[cur][r] + got * cost;
+      int lo, hi;
+      if (r < rest) {   // after the workers of the other part that are free no later
+        lo = rest, hi = workers;
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          if (free_at[cur][mid] + full * cost <= mine) lo = mid + 1; else hi = mid;
+        }
+        new_rank = r + (lo - rest);
+      } else {          // after the workers of the other part that are free strictly earlier
+        lo = 0, hi = rest;
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          if (free_at[cur][mid] + (full + 1) * cost < mine) lo = mid + 1; else hi = mid;
+        }
+        new_rank = (r - rest) + lo;
+      }
+    }
+    __syncthreads();   // everybody has read count[] and this buffer
+    if (r < workers) {
+      count[me] += got;
+      free_at[cur ^ 1][new_rank] = mine;
+      who[cur ^ 1][new_rank] = me;
     }
     __syncthreads();
   }
-  if (w < workers) sched_count[w] = count[w];
+  if (r < workers) sched_count[r] = count[r];
 }
 
 // Maps, arguments and launch shared by the two entry points.  The tensor maps see a as [a_map_rows, a_row_bytes] and b
