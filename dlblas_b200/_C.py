@@ -63,6 +63,8 @@ SIGNATURES = {
     "dlb_p2p_push_rows_indexed": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_vp, c_vp]),
     "dlb_grouped_gemm_16bit": (c_int, [c_vp, c_vp, c_int, c_i64, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_vp, c_i64,
                                        c_vp, c_vp]),
+    "dlb_grouped_gemm_16bit_b_kn": (c_int, [c_vp, c_vp, c_int, c_i64, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_vp,
+                                            c_i64, c_vp, c_vp]),
     "dlb_k_grouped_gemm_workspace_bytes": (c_i64, [c_i64, c_i64, c_i64, c_int, c_int]),
     "dlb_k_grouped_gemm_16bit": (c_int, [c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_int, c_int, c_vp, c_i64, c_vp,
                                          c_vp, c_vp]),

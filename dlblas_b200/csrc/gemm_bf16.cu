@@ -66,6 +66,7 @@ struct Args16 {
   const int* sched_count;
   int sched_stride;
   int b_group_rows;
+  bool b_mn;           // kseg null: B is [groups, k, n] (MN-major, b_group_rows = k) instead of [groups, n, k]
   long long c_group_rows;
   uint32_t idesc;
   int* status;
@@ -301,18 +302,30 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         const int kx = kb * UMMA_BK_BYTES;
         const int a_row = ti.row0;
         const int b_row = ti.n0 + ti.e * g.b_group_rows;
+        // B as [groups, k, n] (b_mn): boxes of 64 K rows x 64 columns at row e * k + 64 kb, as for k-grouped launches
+        const int bx = 2 * (ti.n0 + (int)rank * (BN / CTAS)), by = ti.e * g.b_group_rows + kb * 64;
         if constexpr (PAIR) {
           const uint32_t lead_full = mapa(full_bar(s), 0);
           if (elect_one()) {
             if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);      // the loads of both CTAs
             tma_load_2d_pair(a_dst, &tmap_a, kx, a_row + (int)rank * BM, lead_full);
-            tma_load_2d_pair(b_dst, &tmap_b, kx, b_row + (int)rank * (BN / 2), lead_full);
+            if (g.b_mn) {
+#pragma unroll
+              for (int c = 0; c < BN / 2 / 64; ++c) tma_load_2d_pair(b_dst + c * 8192, &tmap_b, bx + 128 * c, by, lead_full);
+            } else {
+              tma_load_2d_pair(b_dst, &tmap_b, kx, b_row + (int)rank * (BN / 2), lead_full);
+            }
           }
         } else if (elect_one()) {
           mbar_expect_tx(full_bar(s), STAGE_BYTES);
           tma_load_2d(a_dst, &tmap_a, kx, a_row, full_bar(s));
-          tma_load_2d(b_dst, &tmap_b, kx, b_row, full_bar(s));
-          tma_load_2d(b_dst + 128 * UMMA_BK_BYTES, &tmap_b, kx, b_row + 128, full_bar(s));
+          if (g.b_mn) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(b_dst + c * 8192, &tmap_b, bx + 128 * c, by, full_bar(s));
+          } else {
+            tma_load_2d(b_dst, &tmap_b, kx, b_row, full_bar(s));
+            tma_load_2d(b_dst + 128 * UMMA_BK_BYTES, &tmap_b, kx, b_row + 128, full_bar(s));
+          }
         }
         __syncwarp();
       }
@@ -376,20 +389,22 @@ gemm16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         }
         tc_fence_after();
         const uint32_t a_addr = smem_base + s * STAGE_BYTES;
+        const bool b_mn = mn || g.b_mn;
         const uint64_t a_desc = mn ? make_smem_desc_mn(a_addr) : make_smem_desc(a_addr);
-        const uint64_t b_desc = mn ? make_smem_desc_mn(a_addr + A_STAGE_BYTES) : make_smem_desc(a_addr + A_STAGE_BYTES);
-        const uint32_t kstep = mn ? (2048u >> 4) : 2u;   // 16 K: two 8-row swizzle atoms / 32 bytes along the row
+        const uint64_t b_desc = b_mn ? make_smem_desc_mn(a_addr + A_STAGE_BYTES) : make_smem_desc(a_addr + A_STAGE_BYTES);
+        // 16 K further on: two 8-row swizzle atoms (MN-major) or 32 bytes along the row (K-major)
+        const uint32_t kstep_a = mn ? (2048u >> 4) : 2u, kstep_b = b_mn ? (2048u >> 4) : 2u;
         if (elect_one()) {
           if constexpr (PAIR) {
 #pragma unroll
             for (int kk = 0; kk < UMMA_BK_BYTES / 32; ++kk)
-              tc_mma_f16_pair(d_tmem, a_desc + kstep * kk, b_desc + kstep * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              tc_mma_f16_pair(d_tmem, a_desc + kstep_a * kk, b_desc + kstep_b * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             tc_commit_pair(empty_bar(s));                          // frees the stage in both CTAs
             if (kb == nkb - 1) tc_commit_pair(tfull_bar(b));       // both CTAs' drain warps
           } else {
 #pragma unroll
             for (int kk = 0; kk < UMMA_BK_BYTES / 32; ++kk)
-              tc_mma_f16(d_tmem, a_desc + kstep * kk, b_desc + kstep * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              tc_mma_f16(d_tmem, a_desc + kstep_a * kk, b_desc + kstep_b * kk, g.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             tc_commit(empty_bar(s));
             if (kb == nkb - 1) tc_commit(tfull_bar(b));
           }
@@ -649,16 +664,16 @@ k_group_schedule_kernel(const int4* __restrict__ kseg, int groups, int tiles_per
 
 // Maps, arguments and launch shared by the two entry points.  The tensor maps see a as [a_map_rows, a_row_bytes] and b
 // as [b_map_rows, b_row_bytes] with boxes of box_rows rows; m rows (columns when kseg is given) of A meet n of B.
-static int run_gemm16(const void* a, int64_t a_map_rows, int64_t a_row_bytes, const void* b, int64_t b_map_rows,
-                      int64_t b_row_bytes, int box_rows, int dtype, int64_t m, int64_t n, int64_t k, const int4* kseg,
-                      int b_group_rows, long long c_group_rows, const int32_t* tiles, int max_tiles, int tile_rows,
-                      void* c, int64_t ldc, int32_t* status, void* stream, const int* sched = nullptr,
-                      const int* sched_count = nullptr, int sched_stride = 0) {
+static int run_gemm16(const void* a, int64_t a_map_rows, int64_t a_row_bytes, int a_box_rows, const void* b,
+                      int64_t b_map_rows, int64_t b_row_bytes, int b_box_rows, int dtype, int64_t m, int64_t n, int64_t k,
+                      const int4* kseg, bool b_mn, int b_group_rows, long long c_group_rows, const int32_t* tiles,
+                      int max_tiles, int tile_rows, void* c, int64_t ldc, int32_t* status, void* stream,
+                      const int* sched = nullptr, const int* sched_count = nullptr, int sched_stride = 0) {
   int rc = check_device();
   if (rc != DLB_OK) return rc;
   CUtensorMap ma, mb;
-  if ((rc = make_map_box(&ma, a, (uint64_t)a_map_rows, (uint64_t)a_row_bytes, (uint32_t)box_rows)) != DLB_OK) return rc;
-  if ((rc = make_map_box(&mb, b, (uint64_t)b_map_rows, (uint64_t)b_row_bytes, (uint32_t)box_rows)) != DLB_OK) return rc;
+  if ((rc = make_map_box(&ma, a, (uint64_t)a_map_rows, (uint64_t)a_row_bytes, (uint32_t)a_box_rows)) != DLB_OK) return rc;
+  if ((rc = make_map_box(&mb, b, (uint64_t)b_map_rows, (uint64_t)b_row_bytes, (uint32_t)b_box_rows)) != DLB_OK) return rc;
   Args16 g = {};
   g.c = c;
   g.ldc = ldc;
@@ -674,12 +689,14 @@ static int run_gemm16(const void* a, int64_t a_map_rows, int64_t a_row_bytes, co
   g.sched_count = sched_count;
   g.sched_stride = sched_stride;
   g.b_group_rows = b_group_rows;
+  g.b_mn = b_mn;
   g.c_group_rows = c_group_rows;
   const int ctas = tile_rows / BM;
   g.num_m_tiles_static = (int)ceil_div(m, (int64_t)tile_rows);
   g.num_n_tiles = (int)ceil_div(n, (int64_t)BN);
   g.idesc = make_idesc16(dtype == DLB_BF16 ? 1u : 0u, ctas);
-  if (kseg != nullptr) g.idesc |= (1u << 15) | (1u << 16);   // A and B MN-major
+  if (kseg != nullptr) g.idesc |= 1u << 15;            // A MN-major
+  if (kseg != nullptr || b_mn) g.idesc |= 1u << 16;    // B MN-major
   g.status = status;
   g.timeout_cycles = wait_limit_cycles(DEFAULT_TIMEOUT_CYCLES);
   const int workers = sm_count() / ctas;
@@ -699,9 +716,10 @@ static int run_gemm16(const void* a, int64_t a_map_rows, int64_t a_row_bytes, co
 
 using namespace dlb;
 
-extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t rows, int num_groups, int64_t n,
-                                      int64_t k, const int32_t* tiles, int max_tiles, int tile_rows, void* c,
-                                      int64_t ldc, int32_t* status, void* stream) {
+// b_kn: B is [num_groups, k, n] (read as an MN-major operand) instead of [num_groups, n, k]
+static int grouped_gemm_16bit(const void* a, const void* b, bool b_kn, int dtype, int64_t rows, int num_groups, int64_t n,
+                              int64_t k, const int32_t* tiles, int max_tiles, int tile_rows, void* c, int64_t ldc,
+                              int32_t* status, void* stream) {
   DLB_REQUIRE(rows >= 0 && n > 0 && k > 0 && num_groups > 0, DLB_ERR_INVALID,
               "grouped_gemm_16bit: bad sizes rows=%lld n=%lld k=%lld groups=%d", (long long)rows, (long long)n,
               (long long)k, num_groups);
@@ -709,8 +727,12 @@ extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, i
   DLB_REQUIRE(k % 8 == 0 && n % 8 == 0 && ldc % 8 == 0, DLB_ERR_INVALID,
               "grouped_gemm_16bit: k=%lld, n=%lld and ldc=%lld must be multiples of 8 (16-byte rows)", (long long)k,
               (long long)n, (long long)ldc);
-  DLB_REQUIRE(rows < (1ll << 31) && (long long)num_groups * n < (1ll << 31) && 2 * k < (1ll << 31), DLB_ERR_INVALID,
-              "grouped_gemm_16bit: size too large");
+  DLB_REQUIRE(!b_kn || k % 64 == 0, DLB_ERR_INVALID,
+              "grouped_gemm_16bit: b as [groups, k, n] needs k=%lld to be a multiple of 64 (a K block must not run into "
+              "the next group's rows)", (long long)k);
+  DLB_REQUIRE(rows < (1ll << 31) && (long long)num_groups * n < (1ll << 31) && (long long)num_groups * k < (1ll << 31) &&
+                  2 * k < (1ll << 31) && 2 * n < (1ll << 31),
+              DLB_ERR_INVALID, "grouped_gemm_16bit: size too large");
   DLB_REQUIRE(tiles != nullptr || num_groups == 1, DLB_ERR_INVALID, "grouped_gemm_16bit: several groups need a tile list");
   DLB_REQUIRE(tile_rows == 128 || tile_rows == 256, DLB_ERR_INVALID, "grouped_gemm_16bit: tile_rows must be 128 or 256");
   if (rows == 0 || (tiles != nullptr && max_tiles == 0)) return DLB_OK;
@@ -718,8 +740,25 @@ extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, i
   DLB_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 16 == 0) &&
                   ((uintptr_t)tiles % 16 == 0),
               DLB_ERR_INVALID, "grouped_gemm_16bit: a, b, c and tiles must be 16-byte aligned");
-  return run_gemm16(a, rows, 2 * k, b, (int64_t)num_groups * n, 2 * k, 128, dtype, rows, n, k, nullptr, (int)n, 0, tiles,
-                    max_tiles, tile_rows, c, ldc, status, stream);
+  if (b_kn)
+    return run_gemm16(a, rows, 2 * k, 128, b, (int64_t)num_groups * k, 2 * n, 64, dtype, rows, n, k, nullptr, true, (int)k,
+                      0, tiles, max_tiles, tile_rows, c, ldc, status, stream);
+  return run_gemm16(a, rows, 2 * k, 128, b, (int64_t)num_groups * n, 2 * k, 128, dtype, rows, n, k, nullptr, false, (int)n,
+                    0, tiles, max_tiles, tile_rows, c, ldc, status, stream);
+}
+
+extern "C" int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t rows, int num_groups, int64_t n,
+                                      int64_t k, const int32_t* tiles, int max_tiles, int tile_rows, void* c,
+                                      int64_t ldc, int32_t* status, void* stream) {
+  return grouped_gemm_16bit(a, b, false, dtype, rows, num_groups, n, k, tiles, max_tiles, tile_rows, c, ldc, status,
+                            stream);
+}
+
+extern "C" int dlb_grouped_gemm_16bit_b_kn(const void* a, const void* b, int dtype, int64_t rows, int num_groups,
+                                           int64_t n, int64_t k, const int32_t* tiles, int max_tiles, int tile_rows,
+                                           void* c, int64_t ldc, int32_t* status, void* stream) {
+  return grouped_gemm_16bit(a, b, true, dtype, rows, num_groups, n, k, tiles, max_tiles, tile_rows, c, ldc, status,
+                            stream);
 }
 
 // Workspace of dlb_k_grouped_gemm_16bit, in bytes: the tile list, the K ranges and the workers' tile lists.
@@ -777,7 +816,7 @@ extern "C" int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype,
   k_group_schedule_kernel<<<1, 256, 0, st>>>(kseg, num_groups, (int)per_group, workers, sched, sched_count, sched_stride);
   if ((rc = check_cuda(cudaGetLastError(), "k_group_schedule_kernel")) != DLB_OK) return rc;
   count_launch();
-  return run_gemm16(a, k_total, 2 * m, b, k_total, 2 * n, 64, dtype, m, n, 64, kseg, 0, m,
+  return run_gemm16(a, k_total, 2 * m, 64, b, k_total, 2 * n, 64, dtype, m, n, 64, kseg, false, 0, m,
                     reinterpret_cast<const int32_t*>(tiles), (int)(num_groups * m_tiles), tile_rows, c, n, status, stream,
                     sched, sched_count, sched_stride);
 }

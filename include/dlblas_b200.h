@@ -269,6 +269,11 @@ DLB_API int dlb_p2p_push_rows_indexed(const void* src, int64_t row_bytes, int64_
 DLB_API int dlb_grouped_gemm_16bit(const void* a, const void* b, int dtype, int64_t rows, int num_groups, int64_t n,
                            int64_t k, const int32_t* tiles, int max_tiles, int tile_rows, void* c, int64_t ldc,
                            int32_t* status, void* stream);
+/* The same with b as [num_groups, k, n] (m_grouped_gemm's default, trans_b = False): the tensor cores read b as an
+ * MN-major operand, nothing is transposed.  k must be a multiple of 64. */
+DLB_API int dlb_grouped_gemm_16bit_b_kn(const void* a, const void* b, int dtype, int64_t rows, int num_groups, int64_t n,
+                                int64_t k, const int32_t* tiles, int max_tiles, int tile_rows, void* c, int64_t ldc,
+                                int32_t* status, void* stream);
 
 /* k_grouped_gemm (dlblas/kernels/grouped_gemm/BF16/k_grouped_gemm.py:126-176, :254-330): groups along the reduction
  * dimension.  a [k_total, m] and b [k_total, n] row-major bf16 or fp16; group g owns the next group_sizes[g] rows of

@@ -49,6 +49,15 @@ def test_m_grouped_gemm_large_and_empty():
         del os.environ["DLBLAS_GEMM16_TILE_ROWS"]
     _C.check_status()
     assert torch.equal(out, out1)                                # same sums in the same order
+    b_kn = b.transpose(1, 2).contiguous()                        # [G, K, N]: read as an MN-major operand, no transposition
+    for tile_rows in ("128", "256"):
+        os.environ["DLBLAS_GEMM16_TILE_ROWS"] = tile_rows
+        try:
+            out2 = m_grouped_gemm(a, b_kn, sizes, trans_b=False)
+        finally:
+            del os.environ["DLBLAS_GEMM16_TILE_ROWS"]
+        _C.check_status()
+        assert torch.equal(out, out2)
     empty = m_grouped_gemm(a[:0], b, torch.zeros(4, dtype=torch.int64, device=DEV), trans_b=True)
     assert empty.shape == (0, 1024)
 
