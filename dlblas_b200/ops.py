@@ -184,6 +184,21 @@ def grouped_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch
 
 
 # --------------------------------------------------------------------------- combine
+def grouped_gemm_16bit(a: torch.Tensor, b: torch.Tensor, tiles: torch.Tensor, max_tiles: int, tile_rows: int,
+                       out: torch.Tensor) -> torch.Tensor:
+    """out[rows of group g] = a[rows of g] @ b[g]^T on bf16 / fp16 operands, a [rows, k], b [groups, n, k]; `tiles` from
+    build_tiles with the same tile_rows."""
+    require_cuda(a, b, tiles, out)
+    assert a.dtype == b.dtype == out.dtype and a.dtype in (torch.bfloat16, torch.float16)
+    assert a.is_contiguous() and b.is_contiguous() and out.stride(-1) == 1
+    rows, k = a.shape
+    groups, n, bk = b.shape
+    assert bk == k and out.shape == (rows, n)
+    check(lib().dlb_grouped_gemm_16bit(ptr(a), ptr(b), dtype_code(a.dtype), rows, groups, n, k, ptr(tiles), max_tiles,
+                                       tile_rows, ptr(out), out.stride(0), ptr(_C.status_word(a.device)), stream(a.device)))
+    return out
+
+
 def sum_topk(y: torch.Tensor, tokens: int, top_k: int, ids: Optional[torch.Tensor] = None, id_lo: int = 0,
              id_hi: int = 0, skip_unrouted_rows: bool = False) -> torch.Tensor:
     """out[t] = sum_j y[t*top_k + j]; with ids, slots whose id is outside [id_lo, id_hi) are skipped."""

@@ -619,6 +619,29 @@ def m_grouped_gemm(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tenso
     return torch.cat(out) if out else a.new_empty(0, b.shape[1] if trans_b else b.shape[2])
 
 
+def fused_moe_16bit(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk_weights: torch.Tensor,
+                    topk_ids: torch.Tensor) -> torch.Tensor:
+    """The unquantised mode of dlblas/kernels/fused_moe_v2.py:375-466 (the vLLM-style `fused_experts`): per (token,
+    slot) with a valid expert id, `c1 = x W1[e]^T` rounded to the 16-bit type, `silu(gate) * up` in fp32 rounded to that
+    type (:413-423 via silu_and_mul), `y = act W2[e]^T` rounded; the token's output is the fp32 sum of
+    `weight * y` over its slots, rounded once.  (The reference multiplies by the routing weight inside the second GEMM
+    before rounding `y` and then sums the rounded rows; the two differ by one bf16 rounding per slot, far inside the
+    test tolerance of tests/kernels/test_fused_moe_v2.py:136, atol = 0.07.)"""
+    m, h = x.shape
+    out = torch.zeros(m, h, dtype=torch.float32)
+    for t in range(m):
+        for j in range(topk_ids.shape[1]):
+            e = int(topk_ids[t, j])
+            if e < 0 or e >= w1.shape[0]:
+                continue
+            c1 = (x[t].float() @ w1[e].float().t()).to(x.dtype).float()
+            n = c1.numel() // 2
+            act = ((c1[:n] / (1.0 + torch.exp(-c1[:n]))) * c1[n:]).to(x.dtype).float()
+            y = (act @ w2[e].float().t()).to(x.dtype).float()
+            out[t] += float(topk_weights[t, j]) * y
+    return out.to(x.dtype)
+
+
 def k_grouped_gemm(a: torch.Tensor, b: torch.Tensor, size_per_group: torch.Tensor) -> torch.Tensor:
     """dlblas/kernels/grouped_gemm/BF16/k_grouped_gemm.py:126-176 against its ground truth `gmm_dw`
     (tests/kernels/grouped_gemm/BF16/test_k_grouped_gemm.py:10-28): c[g] = a_g^T b_g over row groups of the shared

@@ -140,3 +140,31 @@ def test_low_latency_masked_experts_single_rank():
     out2 = normal.forward(x.to(DEV), ow.to(DEV), oids.to(DEV), *_to_dev(w13, w13s, w2, w2s))
     _C.check_status()
     assert O.rel_frobenius(out2.cpu(), ref) < TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_moe_v2_unquantised_mode(dtype):
+    """`fused_moe` with every `use_*` flag off: 16-bit weights and activations on the 16-bit grouped GEMM, with an
+    expert map that hides two experts (their slots contribute nothing), against the CPU oracle."""
+    from dlblas_b200 import _C
+    from dlblas_b200.kernels.fused_moe_v2 import fused_moe
+    g = torch.Generator().manual_seed(5)
+    m, h, inter, e, k = 96, 256, 384, 8, 3
+    x = torch.randn(m, h, generator=g).to(dtype)
+    w1 = (torch.randn(e, 2 * inter, h, generator=g) * 0.06).to(dtype)
+    w2 = (torch.randn(e, h, inter, generator=g) * 0.06).to(dtype)
+    weights, ids = O.softmax_topk(torch.randn(m, e, generator=g), k, True)
+    e_map = torch.arange(e, dtype=torch.int32)
+    e_map[2] = -1
+    e_map[7] = -1
+    local = torch.where(e_map[ids] >= 0, ids, torch.full_like(ids, -1))
+    ref = O.fused_moe_16bit(x, w1, w2, weights, local)
+    out = fused_moe(x.to(DEV), w1.to(DEV), w2.to(DEV), weights.to(DEV), ids.to(DEV), expert_map=e_map.to(DEV),
+                    out_dtype=dtype)
+    _C.check_status()
+    assert out.shape == (m, h) and out.dtype == dtype
+    assert O.rel_frobenius(out.cpu(), ref) < 5e-3
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=0.07, rtol=0)      # the reference test's bound
+    assert fused_moe(x[:0].to(DEV), w1.to(DEV), w2.to(DEV), weights[:0].to(DEV), ids[:0].to(DEV)).shape == (0, h)
+    with pytest.raises(NotImplementedError):
+        fused_moe(x.to(DEV), w1.to(DEV), w2.to(DEV), weights.to(DEV), ids.to(DEV), use_int8_w8a16=True)
