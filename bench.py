@@ -716,6 +716,49 @@ def run_profile_bandwidth(args):
     print("\n".join(rows))
 
 
+def run_profile_timeline(args):
+    """`--profile timeline` (under torchrun for more than one GPU): the benchmarked step on `--tokens` tokens per rank
+    under torch.profiler, CUDA activities only; rank 0 prints the kernels of the last of four profiled steps in launch
+    order with their start (ms from the step's first kernel) and duration.  Times under the profiler run a few percent
+    above the bench's; the table is for shares and for what runs alone."""
+    import torch.distributed as dist
+    from torch.profiler import ProfilerActivity, profile
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    layer = Layer(world, rank, dev, group)
+    x, logits, bias = [t.to(dev) for t in make_tokens(args.tokens, 100 + rank)]
+    for _ in range(5):
+        layer.step(x, logits, bias)
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    steps = 4
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            layer.step(x, logits, bias)
+        torch.cuda.synchronize(dev)
+    if rank == 0:
+        evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+        evs.sort(key=lambda e: e.time_range.start)
+        t_end = evs[-1].time_range.end
+        span = (t_end - evs[0].time_range.start) / steps
+        last = [e for e in evs if e.time_range.start >= t_end - span]
+        t0 = last[0].time_range.start
+        print("| start (ms) | duration (ms) | kernel |\n|---|---|---|")
+        for e in last:
+            print(f"| {(e.time_range.start - t0) / 1e3:.3f} | {(e.time_range.end - e.time_range.start) / 1e3:.3f} | "
+                  f"`{e.name[:100]}` |")
+        print(f"\nstep under the profiler: {span / 1e3:.3f} ms, {world} GPU(s), {args.tokens} tokens per rank")
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_profile_sweep(args):
     """`--profile sweep`: the stand-alone block-scaled GEMM over the 12 shapes of the benchmark set, and the two
     grouped GEMMs of the Mixtral-shaped layer; CUDA events, L2 flushed between launches."""
@@ -880,7 +923,7 @@ def run_decode(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile", default="", choices=["", "gemm1", "gemm2", "dense", "gemm16", "kgrouped", "bandwidth", "sweep"],
+    ap.add_argument("--profile", default="", choices=["", "gemm1", "gemm2", "dense", "gemm16", "kgrouped", "bandwidth", "sweep", "timeline"],
                     help="run only one kernel on a small case (for ncu) and exit")
     ap.add_argument("--experts", type=int, default=32, help="experts of the --profile case")
     ap.add_argument("--gpus", type=int, default=1)
@@ -897,6 +940,8 @@ def main():
         run_profile_bandwidth(args)
     elif args.profile == "sweep":
         run_profile_sweep(args)
+    elif args.profile == "timeline":
+        run_profile_timeline(args)
     elif args.profile:
         run_profile(args)
     elif args.workload == "decode" and args.impl == "b200":

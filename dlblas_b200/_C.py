@@ -45,6 +45,9 @@ SIGNATURES = {
     "dlb_fp8_gemm": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_int, c_vp, c_vp]),
     "dlb_moe_grouped_gemm": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_int, c_vp,
                                      c_int, c_i64, c_vp, c_int, c_f, c_vp, c_vp, c_vp, c_vp]),
+    "dlb_moe_grouped_gemm_window": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_int, c_i64, c_i64, c_vp, c_int, c_int, c_int,
+                                            c_vp, c_int, c_i64, c_vp, c_int, c_f, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64,
+                                            c_int]),
     "dlb_ep_dest_ranks": (c_int, [c_vp, c_int, c_i64, c_int, c_int, c_int, c_vp, c_vp]),
     "dlb_moe_sum_topk": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_vp, c_int, c_i64, c_i64, c_int, c_vp, c_vp]),
     "dlb_ep_gather": (c_int, [c_vp, c_int, c_i64, c_vp, c_vp, c_int, c_vp, c_i64, c_int, c_vp, c_vp]),
@@ -55,6 +58,8 @@ SIGNATURES = {
                                    c_vp, c_vp, c_int, c_vp, c_vp, c_vp]),
     "dlb_p2p_unpack_meta": (c_int, [c_vp, c_int, c_int, c_vp, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
     "dlb_p2p_sum_push": (c_int, [c_vp, c_int, c_vp, c_int, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
+    "dlb_p2p_sum_push_cols": (c_int, [c_vp, c_int, c_vp, c_int, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp, c_i64, c_i64,
+                                      c_int]),
     "dlb_p2p_push_rows": (c_int, [c_vp, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
     "dlb_p2p_barrier": (c_int, [c_vp, c_int, c_int, c_vp, ctypes.c_uint64, c_vp, c_vp]),
     "dlb_p2p_all_gather_small": (c_int, [c_vp, c_i64, c_int, c_int, c_vp, c_vp]),

@@ -66,6 +66,7 @@ struct GemmArgs {
   int n_half;                 // SWIGLU_QUANT: intermediate size (n / 2)
   int num_m_tiles_static;
   int num_n_tiles;
+  int n_tile0;   // first n tile of the launch (a launch may cover a window of the columns; 0 otherwise)
   const long long* sorted_idx;
   const float* weights;
   int* status;
@@ -123,7 +124,7 @@ __device__ __forceinline__ Tile decode_tile(const GemmArgs& g, int t, int rank =
     ti.row0 += rank * BM;
     ti.rows = min(BM, max(0, ti.rows - rank * BM));
   }
-  ti.n0 = n_tile * (MODE == DLB_EPI_SWIGLU_QUANT ? BN / 2 : BN);
+  ti.n0 = (n_tile + g.n_tile0) * (MODE == DLB_EPI_SWIGLU_QUANT ? BN / 2 : BN);
   return ti;
 }
 
@@ -762,11 +763,13 @@ extern "C" int dlb_fp8_gemm(const void* a, const void* b, const float* a_s, int6
   return launch_typed<DLB_EPI_STORE>(bn, ctas, c_dtype, ma, mb, g, grid, (cudaStream_t)stream);
 }
 
-extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a, const void* b, const float* b_s,
-                                    int num_local_experts, int64_t n, int64_t k, const int32_t* tiles, int max_tiles,
-                                    int tile_rows, int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
-                                    int quant_mode, float quant_eps,
-                                    const int64_t* sorted_idx, const float* weights, int32_t* status, void* stream) {
+// n_begin, n_count: the window of output columns this launch computes (whole tiles of 256; 0, n = everything);
+// sm_margin: SMs left free for kernels of other streams (0 = use them all).
+static int moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a, const void* b, const float* b_s,
+                            int num_local_experts, int64_t n, int64_t k, const int32_t* tiles, int max_tiles,
+                            int tile_rows, int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
+                            int quant_mode, float quant_eps, const int64_t* sorted_idx, const float* weights,
+                            int32_t* status, void* stream, int64_t n_begin, int64_t n_count, int sm_margin) {
   DLB_REQUIRE(rows_a >= 0 && n > 0 && k > 0 && num_local_experts > 0 && max_tiles >= 0, DLB_ERR_INVALID,
               "grouped_gemm: bad sizes rows=%lld n=%lld k=%lld experts=%d", (long long)rows_a, (long long)n,
               (long long)k, num_local_experts);
@@ -784,7 +787,15 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t row
   CUtensorMap ma, mb;
   if ((rc = make_map(&ma, a, (uint64_t)rows_a, (uint64_t)k)) != DLB_OK) return rc;
   if ((rc = make_map(&mb, b, (uint64_t)num_local_experts * (uint64_t)n, (uint64_t)k)) != DLB_OK) return rc;
-  const int sms = sm_count();
+  const bool window = n_begin != 0 || n_count != n;
+  DLB_REQUIRE(n_begin >= 0 && n_count > 0 && n_begin + n_count <= n && n_begin % 256 == 0 &&
+                  (n_count % 256 == 0 || n_begin + n_count == n),
+              DLB_ERR_INVALID, "grouped_gemm: column window [%lld, +%lld) of n=%lld must consist of whole 256-column tiles",
+              (long long)n_begin, (long long)n_count, (long long)n);
+  DLB_REQUIRE(!window || epilogue != DLB_EPI_SWIGLU_QUANT, DLB_ERR_INVALID,
+              "grouped_gemm: the swiglu epilogue pairs gate and up columns and takes no column window");
+  DLB_REQUIRE(sm_margin >= 0 && sm_margin < sm_count(), DLB_ERR_INVALID, "grouped_gemm: sm_margin=%d", sm_margin);
+  const int sms = sm_count() - sm_margin;
   GemmArgs g = {};
   g.a_s = a_s;
   g.a_s_rs = k / 128;
@@ -821,8 +832,9 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t row
     if (epilogue == DLB_EPI_SCATTER_WEIGHT)
       DLB_REQUIRE(sorted_idx && weights, DLB_ERR_INVALID, "grouped_gemm: scatter epilogue needs sorted_idx and weights");
     DLB_REQUIRE(ldc % 8 == 0, DLB_ERR_INVALID, "grouped_gemm: ldc must be a multiple of 8");
-    if (ctas == 1 && (long long)max_tiles * ceil_div(n, 256) < sms) bn = 128;
-    g.num_n_tiles = (int)ceil_div(n, bn);
+    if (!window && ctas == 1 && (long long)max_tiles * ceil_div(n, 256) < sms) bn = 128;
+    g.num_n_tiles = (int)ceil_div(n_count, bn);
+    g.n_tile0 = (int)(n_begin / bn);
   }
   const long long total = (long long)max_tiles * g.num_n_tiles;
   const int workers = sms / ctas;
@@ -832,4 +844,24 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t row
   if (epilogue == DLB_EPI_SCATTER_WEIGHT)
     return launch_typed<DLB_EPI_SCATTER_WEIGHT>(bn, ctas, c_dtype, ma, mb, g, grid, st);
   return launch_typed<DLB_EPI_SWIGLU_QUANT>(bn, ctas, c_dtype, ma, mb, g, grid, st);
+}
+
+extern "C" int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a, const void* b, const float* b_s,
+                                    int num_local_experts, int64_t n, int64_t k, const int32_t* tiles, int max_tiles,
+                                    int tile_rows, int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
+                                    int quant_mode, float quant_eps,
+                                    const int64_t* sorted_idx, const float* weights, int32_t* status, void* stream) {
+  return moe_grouped_gemm(a, a_s, rows_a, b, b_s, num_local_experts, n, k, tiles, max_tiles, tile_rows, epilogue, c,
+                          c_dtype, ldc, q_scale, quant_mode, quant_eps, sorted_idx, weights, status, stream, 0, n, 0);
+}
+
+extern "C" int dlb_moe_grouped_gemm_window(const void* a, const float* a_s, int64_t rows_a, const void* b,
+                                           const float* b_s, int num_local_experts, int64_t n, int64_t k,
+                                           const int32_t* tiles, int max_tiles, int tile_rows, int epilogue, void* c,
+                                           int c_dtype, int64_t ldc, float* q_scale, int quant_mode, float quant_eps,
+                                           const int64_t* sorted_idx, const float* weights, int32_t* status,
+                                           void* stream, int64_t n_begin, int64_t n_count, int sm_margin) {
+  return moe_grouped_gemm(a, a_s, rows_a, b, b_s, num_local_experts, n, k, tiles, max_tiles, tile_rows, epilogue, c,
+                          c_dtype, ldc, q_scale, quant_mode, quant_eps, sorted_idx, weights, status, stream, n_begin,
+                          n_count, sm_margin);
 }

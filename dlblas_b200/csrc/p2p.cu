@@ -144,7 +144,7 @@ template <typename T>
 __global__ void __launch_bounds__(THREADS) sum_push_kernel(const T* __restrict__ y, const long long* __restrict__ ids,
                                                            int top_k, long long h, const int* __restrict__ counts,
                                                            int world, int my_rank, long long region_rows,
-                                                           PeerPtrs peer_dst) {
+                                                           PeerPtrs peer_dst, long long col_begin, long long col_end) {
   const int lane = threadIdx.x & 31;
   const long long rows = (long long)world * region_rows;
   const long long warps = (long long)gridDim.x * (THREADS / 32);
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(THREADS) sum_push_kernel(const T* __restrict__
     const bool mine = lane < top_k && ids[r * top_k + lane] >= 0;
     const unsigned live = __ballot_sync(0xffffffffu, mine);
     T* dst = reinterpret_cast<T*>(peer_dst.p[s]) + ((long long)my_rank * region_rows + j) * h;
-    for (long long c = (long long)lane * 8; c < h; c += 256) {
+    for (long long c = col_begin + (long long)lane * 8; c < col_end; c += 256) {
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -379,31 +379,52 @@ extern "C" int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32
   return DLB_OK;
 }
 
-extern "C" int dlb_p2p_sum_push(const void* y, int dtype, const int64_t* ids, int top_k, int64_t h, const int32_t* counts,
-                                int world, int my_rank, int64_t region_rows, const void* const* peer_dst, void* stream) {
+// col_begin, col_count: the columns of every row that this call sums and stores (multiples of 8; 0, h = all);
+// max_blocks > 0 caps the grid, for a call that shares the GPU with a kernel of another stream.
+static int p2p_sum_push(const void* y, int dtype, const int64_t* ids, int top_k, int64_t h, const int32_t* counts,
+                        int world, int my_rank, int64_t region_rows, const void* const* peer_dst, void* stream,
+                        int64_t col_begin, int64_t col_count, int max_blocks) {
   DLB_REQUIRE(world > 0 && world <= MAX_WORLD && my_rank >= 0 && my_rank < world && region_rows > 0, DLB_ERR_INVALID,
               "p2p_sum_push: bad world / rank / region");
   DLB_REQUIRE(top_k > 0 && top_k <= 32 && h > 0 && h % 8 == 0, DLB_ERR_INVALID,
               "p2p_sum_push: top_k=%d must be in [1, 32] and h=%lld a multiple of 8", top_k, (long long)h);
+  DLB_REQUIRE(col_begin >= 0 && col_count > 0 && col_begin + col_count <= h && col_begin % 8 == 0 && col_count % 8 == 0,
+              DLB_ERR_INVALID, "p2p_sum_push: columns [%lld, +%lld) of h=%lld must be multiples of 8 inside the row",
+              (long long)col_begin, (long long)col_count, (long long)h);
   DLB_REQUIRE(dtype == DLB_BF16 || dtype == DLB_F16, DLB_ERR_INVALID, "p2p_sum_push: dtype must be bf16 or fp16");
   DLB_REQUIRE(y && ids && counts, DLB_ERR_INVALID, "p2p_sum_push: null pointer");
   DLB_REQUIRE((uintptr_t)y % 16 == 0, DLB_ERR_INVALID, "p2p_sum_push: y must be 16-byte aligned");
   PeerPtrs pd;
   int rc = fill_peers(pd, peer_dst, world, "p2p_sum_push");
   if (rc != DLB_OK) return rc;
-  const int grid = grid_for((long long)world * region_rows * 32);
+  int grid = grid_for((long long)world * region_rows * 32);
+  if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == DLB_BF16)
     sum_push_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(y),
                                                             reinterpret_cast<const long long*>(ids), top_k, h, counts,
-                                                            world, my_rank, region_rows, pd);
+                                                            world, my_rank, region_rows, pd, col_begin,
+                                                            col_begin + col_count);
   else
     sum_push_kernel<__half><<<grid, THREADS, 0, st>>>(reinterpret_cast<const __half*>(y),
                                                      reinterpret_cast<const long long*>(ids), top_k, h, counts, world,
-                                                     my_rank, region_rows, pd);
+                                                     my_rank, region_rows, pd, col_begin, col_begin + col_count);
   count_launch();
   DLB_CHECK_LAUNCH("sum_push_kernel");
   return DLB_OK;
+}
+
+extern "C" int dlb_p2p_sum_push(const void* y, int dtype, const int64_t* ids, int top_k, int64_t h, const int32_t* counts,
+                                int world, int my_rank, int64_t region_rows, const void* const* peer_dst, void* stream) {
+  return p2p_sum_push(y, dtype, ids, top_k, h, counts, world, my_rank, region_rows, peer_dst, stream, 0, h, 0);
+}
+
+extern "C" int dlb_p2p_sum_push_cols(const void* y, int dtype, const int64_t* ids, int top_k, int64_t h,
+                                     const int32_t* counts, int world, int my_rank, int64_t region_rows,
+                                     const void* const* peer_dst, void* stream, int64_t col_begin, int64_t col_count,
+                                     int max_blocks) {
+  return p2p_sum_push(y, dtype, ids, top_k, h, counts, world, my_rank, region_rows, peer_dst, stream, col_begin,
+                      col_count, max_blocks);
 }
 
 extern "C" int dlb_p2p_barrier(const void* const* peer_signals, int world, int my_rank, uint32_t* counter,

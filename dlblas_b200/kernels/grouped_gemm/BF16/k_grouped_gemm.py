@@ -30,8 +30,8 @@ def k_grouped_gemm(A: Tensor, B: Tensor, size_per_group: torch.Tensor) -> Tensor
     if num_groups == 0 or M == 0 or N == 0:
         return C
     sizes = size_per_group.to(torch.int64).contiguous()
-    # pairs of CTAs on 256-row tiles of C when M fills them; DLBLAS_GEMM16_TILE_ROWS = 128 / 256 overrides
-    tile_rows = int(os.environ.get("DLBLAS_GEMM16_TILE_ROWS", "256" if M % 256 == 0 else "128"))
+    # pairs of CTAs on 256-row tiles of C unless M is smaller than one; DLBLAS_GEMM16_TILE_ROWS = 128 / 256 overrides
+    tile_rows = int(os.environ.get("DLBLAS_GEMM16_TILE_ROWS", "256" if M >= 256 else "128"))
     need = lib().dlb_k_grouped_gemm_workspace_bytes(K, M, N, num_groups, tile_rows)
     assert need > 0, "k_grouped_gemm: bad sizes"
     work = torch.empty(need, dtype=torch.uint8, device=A.device)

@@ -209,6 +209,22 @@ class FusedMoENormal:
         (rq, rs), rids, rw = d.dispatch_from_hidden(hs, topk_ids, topk_weights, self.block_size,
                                                     while_in_flight=self.during_dispatch)
         fused = os.environ.get("DLBLAS_EP_FUSED_COMBINE", "1") == "1"
+        # DLBLAS_EP_W2_PARTS = p > 1: the second GEMM runs in p launches over windows of the hidden dimension, and the
+        # rows' finished columns are summed and pushed back from a second stream while the next window is computed on
+        # the other SMs (DLBLAS_EP_PUSH_SMS of them, default 16, are left to the push).
+        parts = int(os.environ.get("DLBLAS_EP_W2_PARTS", "1"))
+        if fused and parts > 1 and hs.shape[-1] % (256 * parts) == 0:
+            push_sms = int(os.environ.get("DLBLAS_EP_PUSH_SMS", "16"))
+
+            def push(y, col_begin, col_count):
+                last = col_begin + col_count == hs.shape[-1]
+                d.push_slot_columns(y, rids, col_begin, col_count, 0 if last else push_sms * 8)
+
+            moe_expert_forward(None, rq, rs, up_weights, up_scale, down_weights, down_scale, rw, rids,
+                               topk_ids.shape[1], hs.dtype, 0, self.num_local_experts, _C.QUANT_DIV_EPS,
+                               skip_unrouted_rows=True, return_slot_rows=True, w2_column_parts=parts,
+                               on_columns_done=push, sm_margin=push_sms)
+            return d.finish_pushed_columns(hs.dtype, while_in_flight=self.during_combine)
         out_rows = moe_expert_forward(None, rq, rs, up_weights, up_scale, down_weights, down_scale, rw, rids,
                                       topk_ids.shape[1], hs.dtype, 0, self.num_local_experts,
                                       _C.QUANT_DIV_EPS, skip_unrouted_rows=True, return_slot_rows=fused)

@@ -28,11 +28,17 @@ def moe_expert_forward(hidden: Optional[torch.Tensor], x_q: Optional[torch.Tenso
                        expert_offset: int = 0, num_experts: Optional[int] = None,
                        quant_mode: int = _C.QUANT_RECIP_MUL, weighted_combine: bool = False,
                        fuse_swiglu: bool = True, group_size: int = 128,
-                       skip_unrouted_rows: bool = False, return_slot_rows: bool = False) -> torch.Tensor:
+                       skip_unrouted_rows: bool = False, return_slot_rows: bool = False,
+                       w2_column_parts: int = 1, on_columns_done=None, sm_margin: int = 0) -> torch.Tensor:
     """Expert computation for tokens that are either unquantised (`hidden` [M, H]) or already
     quantised (`x_q` e4m3 [M, H], `x_s` fp32 [M, H/128]).  topk_ids are global ids in
     [expert_offset, expert_offset + E_local) for the experts held in w1/w2; any other id (e.g. -1)
-    contributes zero.  Returns [M, H] of out_dtype."""
+    contributes zero.  Returns [M, H] of out_dtype.
+
+    With `return_slot_rows` and `w2_column_parts` > 1 the second GEMM runs in that many launches over windows of the
+    hidden dimension; `on_columns_done(y, col_begin, col_count)` is called after each launch has been queued (the
+    expert-parallel combine pushes those columns back from another stream), and every launch but the first leaves
+    `sm_margin` SMs to that stream."""
     assert group_size == 128, "block size 128 is the only supported quantisation group"
     e_local, n, h = w1.shape
     inter = n // 2
@@ -70,6 +76,16 @@ def moe_expert_forward(hidden: Optional[torch.Tensor], x_q: Optional[torch.Tenso
         ops.grouped_gemm(a1, a1_s, w1, w1_scale, tiles, max_tiles, _C.EPI_STORE, c1, tile_rows=tile_rows)
         ops.silu_mul_quant(c1, quant_mode, 1e-10, False, None, h_q, h_s)
     y = torch.empty(s_rows, h, dtype=out_dtype, device=dev)
+    parts = w2_column_parts if (return_slot_rows and h % (256 * max(w2_column_parts, 1)) == 0) else 1
+    if parts > 1:
+        step = h // parts
+        for p in range(parts):
+            ops.grouped_gemm(h_q, h_s, w2, w2_scale, tiles, max_tiles, _C.EPI_SCATTER_WEIGHT, y, sorted_idx=sorted_idx,
+                             weights=weights, tile_rows=tile_rows, n_begin=p * step, n_count=step,
+                             sm_margin=sm_margin if p > 0 else 0)
+            if on_columns_done is not None:
+                on_columns_done(y, p * step, step)
+        return y
     ops.grouped_gemm(h_q, h_s, w2, w2_scale, tiles, max_tiles, _C.EPI_SCATTER_WEIGHT, y, sorted_idx=sorted_idx,
                      weights=weights, tile_rows=tile_rows)
     if return_slot_rows:

@@ -658,6 +658,7 @@ class TokenDispatcherP2P:
         self._region_base = (torch.arange(w, device=dev, dtype=torch.int32) * self.region_rows)[None, :]
         self._minus_one = torch.full((1, 1), -1, dtype=torch.int32, device=dev)
         self._ones = torch.ones(self.region_rows, w, dtype=torch.float32, device=dev)
+        self._push_stream = None   # made on first use by push_slot_columns
         torch.cuda.synchronize()
         dist.barrier(group=group)
         self.handle = None
@@ -730,6 +731,33 @@ class TokenDispatcherP2P:
                                           self.hidden_size, _C.ptr(self.recv_counts), w, self.rank, self.region_rows,
                                           self._peers["comb"], _C.stream(dev)))
         return self._finish_combine(within, t, slot_rows.dtype, dev, while_in_flight)
+
+    def push_slot_columns(self, slot_rows: torch.Tensor, recv_ids: torch.Tensor, col_begin: int, col_count: int,
+                          max_blocks: int = 0):
+        """`combine_slots` for columns [col_begin, col_begin + col_count) only, queued on the dispatcher's push stream
+        behind what the current stream has queued so far: the caller goes on computing the remaining columns while
+        these travel.  `max_blocks` caps the push kernel's grid (it shares the GPU with the caller's next kernel).
+        `finish_pushed_columns` must follow the last part."""
+        k = recv_ids.shape[1]
+        assert slot_rows.is_contiguous() and slot_rows.shape == (self.rows * k, self.hidden_size)
+        assert slot_rows.dtype == self.comb.dtype and recv_ids.dtype == torch.int64 and recv_ids.is_contiguous()
+        if self._push_stream is None:
+            self._push_stream = torch.cuda.Stream(device=slot_rows.device)
+        cur = torch.cuda.current_stream(slot_rows.device)
+        self._push_stream.wait_stream(cur)
+        slot_rows.record_stream(self._push_stream)
+        recv_ids.record_stream(self._push_stream)
+        _C.check(_C.lib().dlb_p2p_sum_push_cols(_C.ptr(slot_rows), _C.dtype_code(slot_rows.dtype), _C.ptr(recv_ids), k,
+                                               self.hidden_size, _C.ptr(self.recv_counts), self.world_size, self.rank,
+                                               self.region_rows, self._peers["comb"], self._push_stream.cuda_stream,
+                                               int(col_begin), int(col_count), int(max_blocks)))
+
+    def finish_pushed_columns(self, dtype, while_in_flight=None) -> torch.Tensor:
+        """Joins the push stream, then barrier and gather as in `combine_slots`."""
+        within, t = self.handle
+        dev = self.comb.device
+        torch.cuda.current_stream(dev).wait_stream(self._push_stream)
+        return self._finish_combine(within, t, dtype, dev, while_in_flight)
 
     def _finish_combine(self, within, t, dtype, dev, while_in_flight=None):
         w = self.world_size

@@ -163,9 +163,11 @@ def grouped_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch
                  max_tiles: int, epilogue: int, c: torch.Tensor, q_scale: Optional[torch.Tensor] = None,
                  sorted_idx: Optional[torch.Tensor] = None, weights: Optional[torch.Tensor] = None,
                  round_dtype: Optional[torch.dtype] = None, quant_mode: int = _C.QUANT_RECIP_MUL,
-                 quant_eps: float = 1e-10, tile_rows: int = 128):
+                 quant_eps: float = 1e-10, tile_rows: int = 128, n_begin: int = 0, n_count: Optional[int] = None,
+                 sm_margin: int = 0):
     """a [rows, k] e4m3 in expert-contiguous order, b [E, n, k]; `tiles` built with the same `tile_rows`;
-    see dlb_moe_grouped_gemm."""
+    see dlb_moe_grouped_gemm.  n_begin / n_count: compute only that window of c's columns; sm_margin: SMs to leave to
+    kernels of other streams."""
     require_cuda(a, b)
     assert a.is_contiguous() and a_s.is_contiguous() and b.is_contiguous() and b_s.is_contiguous()
     assert c.stride(-1) == 1
@@ -175,11 +177,18 @@ def grouped_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch
         cdt = dtype_code(round_dtype or torch.bfloat16)
     else:
         cdt = dtype_code(c.dtype)
-    check(lib().dlb_moe_grouped_gemm(ptr(a), ptr(a_s), rows, ptr(b), ptr(b_s), e, n, k, ptr(tiles), max_tiles,
-                                     int(tile_rows), epilogue,
-                                     ptr(c), cdt, c.stride(0), ptr(q_scale), quant_mode, quant_eps, ptr(sorted_idx),
-                                     ptr(weights),
-                                     ptr(_C.status_word(a.device)), stream(a.device)))
+    if n_begin == 0 and n_count in (None, n) and sm_margin == 0:
+        check(lib().dlb_moe_grouped_gemm(ptr(a), ptr(a_s), rows, ptr(b), ptr(b_s), e, n, k, ptr(tiles), max_tiles,
+                                         int(tile_rows), epilogue,
+                                         ptr(c), cdt, c.stride(0), ptr(q_scale), quant_mode, quant_eps, ptr(sorted_idx),
+                                         ptr(weights),
+                                         ptr(_C.status_word(a.device)), stream(a.device)))
+        return c
+    check(lib().dlb_moe_grouped_gemm_window(ptr(a), ptr(a_s), rows, ptr(b), ptr(b_s), e, n, k, ptr(tiles), max_tiles,
+                                            int(tile_rows), epilogue, ptr(c), cdt, c.stride(0), ptr(q_scale), quant_mode,
+                                            quant_eps, ptr(sorted_idx), ptr(weights), ptr(_C.status_word(a.device)),
+                                            stream(a.device), int(n_begin), int(n if n_count is None else n_count),
+                                            int(sm_margin)))
     return c
 
 

@@ -175,6 +175,15 @@ DLB_API int dlb_moe_grouped_gemm(const void* a, const float* a_s, int64_t rows_a
                          int tile_rows, int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
                          int quant_mode, float quant_eps,
                          const int64_t* sorted_idx, const float* weights, int32_t* status, void* stream);
+/* The same over a window of the output columns: only columns [n_begin, n_begin + n_count) of c are computed (whole
+ * tiles of 256 columns; not with DLB_EPI_SWIGLU_QUANT), on at most (SMs - sm_margin) CTAs, so that a caller can hand
+ * the finished columns to a kernel of another stream (the expert-parallel push of the first half of the hidden
+ * dimension runs on the SMs left free while the second half is computed). */
+DLB_API int dlb_moe_grouped_gemm_window(const void* a, const float* a_s, int64_t rows_a, const void* b, const float* b_s,
+                                int num_local_experts, int64_t n, int64_t k, const int32_t* tiles, int max_tiles,
+                                int tile_rows, int epilogue, void* c, int c_dtype, int64_t ldc, float* q_scale,
+                                int quant_mode, float quant_eps, const int64_t* sorted_idx, const float* weights,
+                                int32_t* status, void* stream, int64_t n_begin, int64_t n_count, int sm_margin);
 
 /* ---- combine -----------------------------------------------------------------
  * out[t, :] = cast(sum_j y[t*top_k + j, :]) with fp32 accumulation in slot order: the
@@ -233,6 +242,11 @@ DLB_API int dlb_p2p_push_rows(const void* src, int64_t row_bytes, const int32_t*
  * dlb_p2p_push_rows does.  y [rows * top_k, h] bf16 / fp16, ids int64 [rows, top_k]. */
 DLB_API int dlb_p2p_sum_push(const void* y, int dtype, const int64_t* ids, int top_k, int64_t h, const int32_t* counts,
                      int world, int my_rank, int64_t region_rows, const void* const* peer_dst, void* stream);
+/* The same for columns [col_begin, col_begin + col_count) of every row (multiples of 8), on at most max_blocks thread
+ * blocks of 256 threads when max_blocks > 0. */
+DLB_API int dlb_p2p_sum_push_cols(const void* y, int dtype, const int64_t* ids, int top_k, int64_t h, const int32_t* counts,
+                          int world, int my_rank, int64_t region_rows, const void* const* peer_dst, void* stream,
+                          int64_t col_begin, int64_t col_count, int max_blocks);
 
 /* Barrier among the ranks (one per GPU) between the push phases above; stands in for the ordering DeepEP's
  * `Buffer.dispatch` / `combine` provide inside the library (dlblas/layers/moe/token_dispatcher.py:345-357, 427-433).

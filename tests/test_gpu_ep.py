@@ -46,13 +46,17 @@ def _worker(rank, world, port, ret):
         sl = slice(rank * nle, (rank + 1) * nle)
         local = [w13[sl].to(dev), w13s[sl].to(dev), w2[sl].to(dev), w2s[sl].to(dev)]
         os.environ["DLBLAS_EP_MAX_TOKENS"] = "256"
-        for backend, low_latency in (("p2p", False), ("p2p-chunked", False), ("nccl", False), ("nccl", True),
-                                     ("p2p", True)):
+        first_p2p = None
+        for backend, low_latency in (("p2p", False), ("p2p-parts", False), ("p2p-chunked", False), ("nccl", False),
+                                     ("nccl", True), ("p2p", True)):
             # two token chunks on two streams (ranks hold 96 and 128 tokens: chunks of 48 / 64)
             os.environ["DLBLAS_EP_MIN_CHUNK_ROWS"] = "32" if backend == "p2p-chunked" else "1024"
             os.environ["DLBLAS_EP_CHUNKS"] = "2" if backend == "p2p-chunked" else "1"
             # the chunked run also takes the unfused combine (sum kernel, then push) so that both stay covered
             os.environ["DLBLAS_EP_FUSED_COMBINE"] = "0" if backend == "p2p-chunked" else "1"
+            # second GEMM in two windows of the hidden dimension, the first window pushed back while the second runs
+            os.environ["DLBLAS_EP_W2_PARTS"] = "2" if backend == "p2p-parts" else "1"
+            parts_run = backend == "p2p-parts"
             backend = backend.split("-")[0]
             os.environ["DLBLAS_EP_BACKEND"] = backend
             layer = build_deepep_moe(low_latency, world, dist.group.WORLD, e, h, 128, k, torch.bfloat16)
@@ -68,6 +72,10 @@ def _worker(rank, world, port, ret):
             _C.check_status(dev)
             err = O.rel_frobenius(out.cpu(), ref)
             assert out.shape == (t, h) and err < 2e-2, (backend, low_latency, err)
+            if backend == "p2p" and not low_latency and first_p2p is None:
+                first_p2p = out.clone()
+            if parts_run:
+                assert torch.equal(out, first_p2p)   # same sums in the same order, column window by column window
             # slots without an expert (id -1) are dropped by every exchange
             out_u = layer.forward(x.to(dev), ow.to(dev), ids_u.to(dev), *local)
             _C.check_status(dev)

@@ -42,8 +42,8 @@ def _problem(world, e, k, h, inter, tokens):
     return xs, ws, idss, refs, local
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_prefill_exchange_with_emulated_ranks(world):
+@pytest.mark.parametrize("world,parts", [(2, 1), (4, 1), (2, 2)])
+def test_prefill_exchange_with_emulated_ranks(world, parts):
     from dlblas_b200 import _C, ops
     from dlblas_b200.layers.moe.kernels.blocked_fp8_fused_moe import moe_expert_forward
     lib = _C.lib()
@@ -82,8 +82,13 @@ def test_prefill_exchange_with_emulated_ranks(world):
         assert int(counts_b[r][:world].sum()) == sum(int((within_all[src][:, r] >= 0).sum()) for src in range(world))
         slot_rows = moe_expert_forward(None, q[r].view(FP8), s[r], *local[r], rw, rids, k, torch.bfloat16, 0, nle,
                                        _C.QUANT_DIV_EPS, skip_unrouted_rows=True, return_slot_rows=True)
-        _C.check(lib.dlb_p2p_sum_push(_C.ptr(slot_rows), _C.dtype_code(slot_rows.dtype), _C.ptr(rids), k, h,
-                                      _C.ptr(counts_b[r]), world, r, region, pcomb, st))
+        if parts == 1:
+            _C.check(lib.dlb_p2p_sum_push(_C.ptr(slot_rows), _C.dtype_code(slot_rows.dtype), _C.ptr(rids), k, h,
+                                          _C.ptr(counts_b[r]), world, r, region, pcomb, st))
+        for p in range(parts if parts > 1 else 0):               # the same, one window of the columns at a time
+            _C.check(lib.dlb_p2p_sum_push_cols(_C.ptr(slot_rows), _C.dtype_code(slot_rows.dtype), _C.ptr(rids), k, h,
+                                               _C.ptr(counts_b[r]), world, r, region, pcomb, st, p * (h // parts),
+                                               h // parts, 8 if p == 0 else 0))
     _C.check_status()
     base = (torch.arange(world, device=DEV, dtype=torch.int32) * region)[None, :]
     for r in range(world):                                     # phase 3: every rank gathers its tokens' results
