@@ -57,5 +57,7 @@ def test_fused_moe_v2_against_oracle():
     w_masked = torch.where(ids >= 4, w, torch.zeros_like(w))
     ref_ep = O.fused_moe_v2(x, w13, w13s, w2, w2s, w_masked, ids)
     assert O.rel_frobenius(out_ep.cpu(), ref_ep) < 2e-2
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(AssertionError):               # e4m3 weights without use_fp8_w8a8: the unquantised mode wants 16-bit
         fused_moe(x.to(DEV), w13.to(DEV), w2.to(DEV), w.to(DEV), ids.to(DEV))
+    with pytest.raises(NotImplementedError):
+        fused_moe(x.to(DEV), w13.to(DEV), w2.to(DEV), w.to(DEV), ids.to(DEV), use_int8_w8a8=True)
