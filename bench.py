@@ -837,13 +837,29 @@ def run_decode(args):
     pop = torch.randperm(E, generator=torch.Generator().manual_seed(77)).float() + 1.0
     logits = (torch.randn(tokens, E, generator=g) + torch.log(pop ** -1.2 / (pop ** -1.2).sum())).to(dev)
 
-    def step():
-        w, ids = ops.route_softmax_topk(logits, TOPK, True)
-        routed = layer.forward(x, w, ids, w13[:nl], w13s[:nl], w2[:nl], w2s[:nl])
+    side = torch.cuda.Stream(dev)
+    overlap_shared = os.environ.get("DLBLAS_BENCH_DECODE_OVERLAP", "1") == "1"
+
+    def shared_expert():
         xq, xs = ops.quant_fp8(x, 128, _C.QUANT_RECIP_MUL, 0.0)
         c1 = ops.fp8_gemm(xq, w13[nl], xs, w13s[nl], torch.bfloat16)
         hq, hs = ops.silu_mul_quant(c1, _C.QUANT_RECIP_MUL)
-        return routed + ops.fp8_gemm(hq, w2[nl], hs, w2s[nl], torch.bfloat16)
+        return ops.fp8_gemm(hq, w2[nl], hs, w2s[nl], torch.bfloat16)
+
+    def step():
+        # the shared expert's four small kernels run on a second stream beside the routed experts' weight streaming
+        cur = torch.cuda.current_stream(dev)
+        if overlap_shared:
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                shared = shared_expert()
+        w, ids = ops.route_softmax_topk(logits, TOPK, True)
+        routed = layer.forward(x, w, ids, w13[:nl], w13s[:nl], w2[:nl], w2s[:nl])
+        if overlap_shared:
+            cur.wait_stream(side)
+        else:
+            shared = shared_expert()
+        return routed + shared
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -856,11 +872,11 @@ def run_decode(args):
     host_free = world == 1 or type(layer.token_dispatcher).__name__ == "TokenDispatcherLowLatencyP2P"
     if host_free:
         try:
-            side = torch.cuda.Stream(dev)
-            side.wait_stream(torch.cuda.current_stream(dev))
-            with torch.cuda.stream(side):
+            warm = torch.cuda.Stream(dev)
+            warm.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(warm):
                 step()
-            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.current_stream(dev).wait_stream(warm)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 graph_out = step()                                # noqa: F841  (kept alive with the graph)

@@ -173,7 +173,9 @@ __global__ void __launch_bounds__(THREADS) silu_and_mul_kernel(const T* __restri
   }
 }
 
-// silu(gate) * up, rounded like the reference, then the 1x128 quantisation of the result.
+// silu(gate) * up, rounded like the reference, then the 1x128 quantisation of the result.  With masked_m (masked
+// layout: blockIdx.y = expert) only the expert's first masked_m[e] rows are visited at all; a decode step holds a few
+// hundred valid rows in a layout of tens of thousands.
 template <typename T>
 __global__ void __launch_bounds__(THREADS) silu_mul_quant_kernel(const T* __restrict__ in, long long rows, long long n,
                                                                  int mode, float eps, int round_silu,
@@ -181,17 +183,18 @@ __global__ void __launch_bounds__(THREADS) silu_mul_quant_kernel(const T* __rest
                                                                  long long rows_per_expert, uint8_t* __restrict__ q,
                                                                  float* __restrict__ scales) {
   const long long vec_per_row = n / 8;
-  const long long total = rows * vec_per_row;
   const long long groups = n / 128;
+  long long row_base = 0, my_rows = rows;
+  if (masked_m != nullptr) {
+    row_base = (long long)blockIdx.y * rows_per_expert;
+    my_rows = min((long long)__ldg(masked_m + blockIdx.y), rows_per_expert);
+  }
+  const long long total = my_rows * vec_per_row;
   for (long long u0 = (long long)blockIdx.x * THREADS; u0 < total; u0 += (long long)gridDim.x * THREADS) {
     const long long u = u0 + threadIdx.x;
-    bool active = u < total;
-    const long long row = active ? u / vec_per_row : 0;
-    const long long c = active ? (u - row * vec_per_row) * 8 : 0;
-    if (active && masked_m != nullptr) {
-      const long long e = row / rows_per_expert;
-      active = (row - e * rows_per_expert) < (long long)__ldg(masked_m + e);
-    }
+    const bool active = u < total;
+    const long long row = row_base + (active ? u / vec_per_row : 0);
+    const long long c = active ? (u % vec_per_row) * 8 : 0;
     float h[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) h[i] = 0.f;
@@ -519,7 +522,14 @@ extern "C" int dlb_silu_mul_quant(const void* gate_up, int dtype, int64_t rows, 
   if (rows == 0) return DLB_OK;
   DLB_REQUIRE(gate_up && q && scales, DLB_ERR_INVALID, "silu_mul_quant: null pointer");
   DLB_REQUIRE((uintptr_t)gate_up % 16 == 0 && (uintptr_t)q % 8 == 0, DLB_ERR_INVALID, "silu_mul_quant: misaligned");
-  const int grid = grid_for(rows * (n / 8));
+  dim3 grid((unsigned)grid_for(rows * (n / 8)));
+  if (masked_m != nullptr) {   // one column of blocks per expert, enough of them for a full expert
+    DLB_REQUIRE(rows % rows_per_expert == 0 && rows / rows_per_expert <= 65535, DLB_ERR_INVALID,
+                "silu_mul_quant: rows=%lld must be a whole number (at most 65535) of experts of %lld rows", (long long)rows,
+                (long long)rows_per_expert);
+    grid = dim3((unsigned)min((long long)ceil_div(rows_per_expert * (n / 8), (int64_t)THREADS), 64ll),
+                (unsigned)(rows / rows_per_expert));
+  }
   cudaStream_t st = (cudaStream_t)stream;
   uint8_t* qq = reinterpret_cast<uint8_t*>(q);
   if (dtype == DLB_BF16)

@@ -106,8 +106,13 @@ class FusedMoELowLatency:
         tiles, max_tiles = ops.build_tiles_masked(valid_rows, rows)
         flat = e_local * rows
 
+        # The masked GEMMs of a decode step stream weights at the HBM rate from far fewer SMs than the GPU has;
+        # DLBLAS_DECODE_SM_MARGIN leaves that many SMs to kernels of other streams (a shared expert's small GEMMs,
+        # which otherwise wait for the persistent CTAs to leave).
+        margin = int(os.environ.get("DLBLAS_DECODE_SM_MARGIN", "0"))
+
         def gemm(a_q, a_s, w, w_s, out):
-            ops.grouped_gemm(a_q, a_s, w, w_s, tiles, max_tiles, _C.EPI_STORE, out)
+            ops.grouped_gemm(a_q, a_s, w, w_s, tiles, max_tiles, _C.EPI_STORE, out, sm_margin=margin)
 
         gate_up = torch.empty((e_local, rows, width), device=dev, dtype=self.out_dtype)
         gemm(DisposibleTensor.maybe_unwrap(x_q).view(flat, hidden), DisposibleTensor.maybe_unwrap(x_s).view(flat, -1),
