@@ -722,7 +722,6 @@ def run_profile_timeline(args):
     order with their start (ms from the step's first kernel) and duration.  Times under the profiler run a few percent
     above the bench's; the table is for shares and for what runs alone."""
     import torch.distributed as dist
-    from torch.profiler import ProfilerActivity, profile
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -738,25 +737,32 @@ def run_profile_timeline(args):
     torch.cuda.synchronize(dev)
     if world > 1:
         dist.barrier()
-    steps = 4
-    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        for _ in range(steps):
-            layer.step(x, logits, bias)
-        torch.cuda.synchronize(dev)
-    if rank == 0:
-        evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
-        evs.sort(key=lambda e: e.time_range.start)
-        t_end = evs[-1].time_range.end
-        span = (t_end - evs[0].time_range.start) / steps
-        last = [e for e in evs if e.time_range.start >= t_end - span]
-        t0 = last[0].time_range.start
-        print("| start (ms) | duration (ms) | kernel |\n|---|---|---|")
-        for e in last:
-            print(f"| {(e.time_range.start - t0) / 1e3:.3f} | {(e.time_range.end - e.time_range.start) / 1e3:.3f} | "
-                  f"`{e.name[:100]}` |")
-        print(f"\nstep under the profiler: {span / 1e3:.3f} ms, {world} GPU(s), {args.tokens} tokens per rank")
+    _print_step_timeline(lambda: layer.step(x, logits, bias), dev, rank, f"{world} GPU(s), {args.tokens} tokens per rank")
     if world > 1:
         dist.destroy_process_group()
+
+
+def _print_step_timeline(step, dev, rank, label, steps=4):
+    """Runs `step` `steps` times under torch.profiler (CUDA activities) and prints, on rank 0, the kernels of the last
+    one in launch order."""
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize(dev)
+    if rank != 0:
+        return
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    evs.sort(key=lambda e: e.time_range.start)
+    t_end = evs[-1].time_range.end
+    span = (t_end - evs[0].time_range.start) / steps
+    last = [e for e in evs if e.time_range.start >= t_end - span]
+    t0 = last[0].time_range.start
+    print("| start (ms) | duration (ms) | kernel |\n|---|---|---|")
+    for e in last:
+        print(f"| {(e.time_range.start - t0) / 1e3:.3f} | {(e.time_range.end - e.time_range.start) / 1e3:.3f} | "
+              f"`{e.name[:100]}` |")
+    print(f"\nstep under the profiler: {span / 1e3:.3f} ms, {label}")
 
 
 def run_profile_sweep(args):
@@ -864,6 +870,13 @@ def run_decode(args):
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize(dev)
+    if args.profile == "timeline":                # `--workload decode --profile timeline`: the eager step, kernel by kernel
+        if world > 1:
+            dist.barrier()
+        _print_step_timeline(step, dev, rank, f"{world} GPU(s), decode shape, eager launches")
+        if world > 1:
+            dist.destroy_process_group()
+        return
     # The layer has no host round trip (one GPU: device-side plan; several ranks: peer-to-peer stores and the
     # extension's own barrier kernel), so the whole step (about 40 short kernels) replays as one CUDA graph on
     # every rank.  With DLBLAS_EP_BACKEND=nccl the all-to-all needs its split sizes on the host and the step runs
@@ -956,6 +969,8 @@ def main():
         run_profile_bandwidth(args)
     elif args.profile == "sweep":
         run_profile_sweep(args)
+    elif args.profile == "timeline" and args.workload == "decode":
+        run_decode(args)
     elif args.profile == "timeline":
         run_profile_timeline(args)
     elif args.profile:

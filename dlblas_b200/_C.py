@@ -62,6 +62,8 @@ SIGNATURES = {
                                       c_int]),
     "dlb_p2p_push_rows": (c_int, [c_vp, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
     "dlb_p2p_barrier": (c_int, [c_vp, c_int, c_int, c_vp, ctypes.c_uint64, c_vp, c_vp]),
+    "dlb_p2p_ll_plan": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp,
+                                c_vp, c_vp, c_vp, c_vp]),
     "dlb_p2p_all_gather_small": (c_int, [c_vp, c_i64, c_int, c_int, c_vp, c_vp]),
     "dlb_p2p_ll_quant_push": (c_int, [c_vp, c_int, c_i64, c_i64, c_i64, c_int, c_f, c_vp, c_vp, c_int, c_int, c_vp, c_vp,
                                       c_vp]),

@@ -175,6 +175,91 @@ __global__ void __launch_bounds__(THREADS) sum_push_kernel(const T* __restrict__
   }
 }
 
+// Index arithmetic of the host-free low-latency exchange, one kernel instead of some thirty small tensor operations.
+// counts [world, cnt_stride] (the all-gathered pair counts: source rank x global expert); ids [pairs] this rank's
+// (token, slot) expert ids (negative: none); rank_in [pairs] the pair's rank among this rank's pairs of the same
+// expert.  Rows of an expert's block on its owner are ordered by source rank and, inside a source, by that rank; a
+// rank's return buffer is ordered by expert, then by that rank.
+//   as a source, per pair: pair_rank / pair_row (owner and row of its [nle * rpe] layout; -1 = not sent: no expert or
+//     the block is full), pair_pos (row of the own return buffer), ids32 (the id, -1 when not sent);
+//   as an owner: masked_m [nle] and, per row of the layout, row_rank / row_pos (source and row of its return buffer,
+//     -1 = unused).
+// Every block first builds the counts and their running sums over the experts in shared memory (a few KB).
+__global__ void __launch_bounds__(THREADS) ll_plan_kernel(const int* __restrict__ counts, int cnt_stride, int world,
+                                                          int experts, int me, int nle, int rpe,
+                                                          const long long* __restrict__ ids,
+                                                          const int* __restrict__ rank_in, int pairs,
+                                                          int* __restrict__ pair_rank, int* __restrict__ pair_row,
+                                                          int* __restrict__ pair_pos, int* __restrict__ ids32,
+                                                          int* __restrict__ masked_m, int* __restrict__ row_rank,
+                                                          int* __restrict__ row_pos) {
+  extern __shared__ int plan_smem[];
+  int* cs = plan_smem;                       // [world][experts] counts
+  int* before = plan_smem + world * experts; // [world][experts] the source's pairs of lower experts
+  for (int i = threadIdx.x; i < world * experts; i += THREADS) {
+    const int r = i / experts;
+    cs[i] = __ldg(counts + (long long)r * cnt_stride + (i - r * experts));
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  for (int r = threadIdx.x >> 5; r < world; r += THREADS / 32) {   // one warp per source: scan over the experts
+    int carry = 0;
+    for (int e0 = 0; e0 < experts; e0 += 32) {
+      const int e = e0 + lane;
+      const int v = e < experts ? cs[r * experts + e] : 0;
+      int incl = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+      }
+      if (e < experts) before[r * experts + e] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  __syncthreads();
+  const int lo = me * nle;
+  const long long stride = (long long)gridDim.x * THREADS;
+  const long long first = (long long)blockIdx.x * THREADS + threadIdx.x;
+  for (long long p = first; p < pairs; p += stride) {
+    const long long id = ids[p];
+    int pr = -1, prow = -1, ppos = -1, kept = -1;
+    if (id >= 0 && id < experts) {
+      const int e = (int)id;
+      int rows_before_me = 0;
+      for (int r = 0; r < me; ++r) rows_before_me += cs[r * experts + e];
+      const int row = rows_before_me + rank_in[p];
+      if (row < rpe) {
+        pr = e / nle;
+        prow = (e - pr * nle) * rpe + row;
+        ppos = before[me * experts + e] + rank_in[p];
+        kept = e;
+      }
+    }
+    pair_rank[p] = pr;
+    pair_row[p] = prow;
+    pair_pos[p] = ppos;
+    ids32[p] = kept;
+  }
+  const long long layout_rows = (long long)nle * rpe;
+  for (long long i = first; i < layout_rows; i += stride) {
+    const int le = (int)(i / rpe), row = (int)(i - (long long)le * rpe);
+    const int e = lo + le;
+    int end = 0, src = -1, first_row = 0;
+    for (int r = 0; r < world; ++r) {
+      const int c = cs[r * experts + e];
+      if (src < 0 && row < end + c) {
+        src = r;
+        first_row = end;
+      }
+      end += c;
+    }
+    row_rank[i] = src;
+    row_pos[i] = src >= 0 ? before[src * experts + e] + (row - first_row) : -1;
+    if (row == 0) masked_m[le] = min(end, rpe);
+  }
+}
+
 // Barrier among the ranks of an expert-parallel group, one rank per GPU.  Rank i owns an array of one 32-bit
 // word per peer; arriving means storing the barrier's number (a counter that every rank advances in step) into
 // word "my rank" of every peer's array with release semantics at system scope, so that everything this rank
@@ -461,6 +546,39 @@ extern "C" int dlb_p2p_all_gather_small(const void* src, int64_t bytes, int worl
                                                                      my_rank, pd);
   count_launch();
   DLB_CHECK_LAUNCH("all_gather_small_kernel");
+  return DLB_OK;
+}
+
+extern "C" int dlb_p2p_ll_plan(const int32_t* counts, int cnt_stride, int world, int num_experts, int my_rank,
+                               int num_local_experts, int rows_per_expert, const int64_t* topk_ids,
+                               const int32_t* rank_in_expert, int64_t pairs, int32_t* pair_rank, int32_t* pair_row,
+                               int32_t* pair_pos, int32_t* ids_sent, int32_t* masked_m, int32_t* row_rank,
+                               int32_t* row_pos, void* stream) {
+  DLB_REQUIRE(world > 0 && world <= MAX_WORLD && my_rank >= 0 && my_rank < world, DLB_ERR_INVALID,
+              "p2p_ll_plan: world=%d (max %d), rank=%d", world, MAX_WORLD, my_rank);
+  DLB_REQUIRE(num_experts > 0 && num_local_experts > 0 && num_experts == num_local_experts * world &&
+                  cnt_stride >= num_experts && rows_per_expert > 0 && pairs >= 0 && pairs < (1ll << 31),
+              DLB_ERR_INVALID, "p2p_ll_plan: experts=%d, local=%d, stride=%d, rows_per_expert=%d, pairs=%lld", num_experts,
+              num_local_experts, cnt_stride, rows_per_expert, (long long)pairs);
+  DLB_REQUIRE(counts && masked_m && row_rank && row_pos && (pairs == 0 || (topk_ids && rank_in_expert && pair_rank &&
+                                                                           pair_row && pair_pos && ids_sent)),
+              DLB_ERR_INVALID, "p2p_ll_plan: null pointer");
+  const size_t smem = (size_t)2 * world * num_experts * sizeof(int);
+  DLB_REQUIRE(smem <= 200 * 1024, DLB_ERR_UNSUPPORTED, "p2p_ll_plan: %d ranks x %d experts do not fit in shared memory",
+              world, num_experts);
+  if (smem > 48 * 1024) {
+    int rc = check_cuda(cudaFuncSetAttribute(ll_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                        "cudaFuncSetAttribute(ll_plan_kernel)");
+    if (rc != DLB_OK) return rc;
+  }
+  const long long work = max((long long)pairs, (long long)num_local_experts * rows_per_expert);
+  const int grid = (int)min((long long)ceil_div(work, (int64_t)THREADS), 128ll);
+  ll_plan_kernel<<<grid, THREADS, smem, (cudaStream_t)stream>>>(
+      counts, cnt_stride, world, num_experts, my_rank, num_local_experts, rows_per_expert,
+      reinterpret_cast<const long long*>(topk_ids), rank_in_expert, (int)pairs, pair_rank, pair_row, pair_pos, ids_sent,
+      masked_m, row_rank, row_pos);
+  count_launch();
+  DLB_CHECK_LAUNCH("ll_plan_kernel");
   return DLB_OK;
 }
 

@@ -83,11 +83,11 @@ class FusedMoELowLatency:
         self.layer_index = layer_index
         self.block_size = block_size
         self.out_dtype = out_dtype
-        # Exchange backend: with more than one rank the default is the peer-to-peer dispatcher (in-kernel stores
-        # into the owners' masked layouts, no host round trip, CUDA-graph capturable); DLBLAS_EP_BACKEND=nccl
-        # selects the all-to-all with host-side split sizes.
-        backend = os.environ.get("DLBLAS_EP_BACKEND", "p2p" if ep_size > 1 else "nccl").lower()
-        cls = TokenDispatcherLowLatencyP2P if (backend == "p2p" and ep_size > 1) else TokenDispatcherLowLatency
+        # Exchange backend: the default is the peer-to-peer dispatcher (in-kernel stores into the owners' masked
+        # layouts, no host round trip, CUDA-graph capturable; on one rank the same kernels on this GPU's own
+        # memory); DLBLAS_EP_BACKEND=nccl selects the all-to-all with host-side split sizes.
+        backend = os.environ.get("DLBLAS_EP_BACKEND", "p2p").lower()
+        cls = TokenDispatcherLowLatencyP2P if backend == "p2p" else TokenDispatcherLowLatency
         self.token_dispatcher = cls(group=ep_group, num_experts=num_experts, num_local_experts=num_experts // ep_size,
                                     hidden_size=hidden_dim, params_dtype=out_dtype)
 

@@ -458,8 +458,9 @@ class TokenDispatcherLowLatencyP2P:
         self.num_local_experts = num_local_experts
         self.hidden_size = hidden_size
         self.params_dtype = params_dtype or torch.bfloat16
-        self.world_size = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        single = group is None or not (dist.is_available() and dist.is_initialized())
+        self.world_size = 1 if single else dist.get_world_size(group)
+        self.rank = 0 if single else dist.get_rank(group)
         assert num_experts == num_local_experts * self.world_size, "experts must split evenly over the ranks"
         assert hidden_size % 128 == 0 and self.params_dtype in (torch.bfloat16, torch.float16)
         self.num_max_dispatch_tokens_per_rank = int(os.getenv("DEEPEP_MAX_TOKENS_PER_RANK",
@@ -471,14 +472,16 @@ class TokenDispatcherLowLatencyP2P:
         self.send_rows = self.num_max_dispatch_tokens_per_rank * self.max_top_k
         sizes = [("allcnt", w * self.cnt_ints * 4), ("q", nle * rpe * h), ("s", nle * rpe * (h // 128) * 4),
                  ("comb", self.send_rows * h * 2)]
-        self._sym = _SymmetricBuffers(group, sizes)
+        # one rank: the same kernels on ordinary device memory ("peer 0" is this GPU), no barrier
+        self._sym = _LocalBuffers(sizes) if self.world_size == 1 else _SymmetricBuffers(group, sizes)
         self.allcnt = self._sym.region("allcnt", w * self.cnt_ints * 4).view(torch.int32).view(w, self.cnt_ints)
         self.recv_q = self._sym.region("q", nle * rpe * h).view(ops.FP8).view(nle, rpe, h)
         self.recv_s = self._sym.region("s", nle * rpe * (h // 128) * 4).view(torch.float32).view(nle, rpe, h // 128)
         self.comb = self._sym.region("comb", self.send_rows * h * 2).view(self.params_dtype).view(self.send_rows, h)
         self.allcnt.zero_()
         torch.cuda.synchronize()
-        dist.barrier(group=group)
+        if self.world_size > 1:
+            dist.barrier(group=group)
         self.handle = None
 
     @property
@@ -519,15 +522,26 @@ class TokenDispatcherLowLatencyP2P:
         _C.check(_C.lib().dlb_p2p_all_gather_small(_C.ptr(counts), self.cnt_ints * 4, w, me, sym.peers["allcnt"],
                                                   _C.stream(dev)))
         sym.barrier(0)
-        c = self.allcnt[:, :e].to(torch.int64)                       # [W(source), E]: a private copy of the counts
-        pair_rank, pair_row, pair_pos, sent, masked_m, row_rank, row_pos = make_low_latency_p2p_plan(
-            c, me, nle, rpe, topk_idx, rank_in)
+        # where every pair goes and where every row of the own layout came from: one kernel on the gathered counts
+        # (the peers overwrite them only after this rank has passed the combine's barrier); the same arithmetic in
+        # plain tensor operations is `make_low_latency_p2p_plan`
+        pairs = t * k
+        plan_ints = torch.empty(4 * pairs + nle + 2 * nle * rpe, dtype=torch.int32, device=dev)
+        pair_rank, pair_row, pair_pos, ids_sent = (plan_ints[i * pairs:(i + 1) * pairs] for i in range(4))
+        masked_m = plan_ints[4 * pairs:4 * pairs + nle]
+        row_rank = plan_ints[4 * pairs + nle:4 * pairs + nle + nle * rpe]
+        row_pos = plan_ints[4 * pairs + nle + nle * rpe:]
+        ids_flat = topk_idx.contiguous().view(-1)
+        _C.check(_C.lib().dlb_p2p_ll_plan(_C.ptr(self.allcnt), self.cnt_ints, w, e, me, nle, rpe, _C.ptr(ids_flat),
+                                          _C.ptr(rank_in), pairs, _C.ptr(pair_rank), _C.ptr(pair_row), _C.ptr(pair_pos),
+                                          _C.ptr(ids_sent), _C.ptr(masked_m), _C.ptr(row_rank), _C.ptr(row_pos),
+                                          _C.stream(dev)))
         _C.check(_C.lib().dlb_p2p_ll_quant_push(
             _C.ptr(hidden_states), _C.dtype_code(hidden_states.dtype), t, hidden_states.shape[1],
             hidden_states.stride(0), _C.QUANT_DIV_EPS, 1e-10, _C.ptr(pair_rank), _C.ptr(pair_row), k, w,
             sym.peers["q"], sym.peers["s"], _C.stream(dev)))
         sym.barrier(0)
-        plan = (pair_pos.view(t, k), sent.view(t, k), row_rank, row_pos, t)
+        plan = (pair_pos.view(t, k), ids_sent.view(t, k), row_rank, row_pos, t, pair_row.view(t, k))
         return [self.recv_q, self.recv_s], masked_m, plan, _record_event(), (lambda: None)
 
     def combine(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor):
@@ -539,25 +553,55 @@ class TokenDispatcherLowLatencyP2P:
                       handle: Tuple, async_finish: bool):
         assert topk_idx.dtype == torch.int64
         assert topk_weights.dtype == torch.float32
-        pair_pos, sent, row_rank, row_pos, t = handle
+        pair_pos, ids_sent, row_rank, row_pos, t, pair_row = handle
         nle, rpe, h = hidden_states.shape
         assert hidden_states.dtype == self.comb.dtype and hidden_states.is_contiguous()
         dev = hidden_states.device
         sym = self._sym
+        out = torch.empty(t, h, dtype=hidden_states.dtype, device=dev)
+        if self.world_size == 1:
+            # one rank: a token's rows are in this GPU's own layout; out[t] = sum_k w[t, k] * layout[pair_row[t, k]]
+            ops.ep_gather(hidden_states.view(nle * rpe, h), ids_sent, topk_weights.contiguous(), pair_row, out)
+            return out, _record_event(), (lambda: None)
         _C.check(_C.lib().dlb_p2p_push_rows_indexed(_C.ptr(hidden_states), h * hidden_states.element_size(), nle * rpe,
                                                    _C.ptr(row_rank), _C.ptr(row_pos), self.world_size,
                                                    sym.peers["comb"], _C.stream(dev)))
         sym.barrier(1)
-        out = torch.empty(t, h, dtype=hidden_states.dtype, device=dev)
-        ids32 = torch.where(sent, topk_idx, torch.full_like(topk_idx, -1)).to(torch.int32).contiguous()
         # out[t] = sum_k w[t, k] * comb[pair_pos[t, k]]
-        ops.ep_gather(self.comb, ids32, topk_weights.contiguous(), pair_pos.contiguous(), out)
+        ops.ep_gather(self.comb, ids_sent, topk_weights.contiguous(), pair_pos, out)
         return out, _record_event(), (lambda: None)
 
 
 # ----------------------------------------------------------------------------------------------
 # normal (prefill) mode over peer-to-peer stores: no host synchronisation, no staging copies
 # ----------------------------------------------------------------------------------------------
+class _LocalBuffers:
+    """Stand-in for `_SymmetricBuffers` on a single rank: one ordinary device allocation cut into the same named
+    regions, this GPU as its only "peer", and no barrier (stream order is the order)."""
+
+    def __init__(self, regions):
+        import ctypes
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.device, self.world_size, self.rank = dev, 1, 0
+        offs, total = {}, 0
+        for name, n in regions:
+            offs[name] = total
+            total += (n + 255) // 256 * 256
+        self._buf = torch.zeros(max(total, 256), dtype=torch.uint8, device=dev)
+        self.offs = offs
+        self.peers = {name: (ctypes.c_void_p * 1)(self._buf.data_ptr() + offs[name]) for name in offs}
+
+    def region(self, name, nbytes):
+        o = self.offs[name]
+        return self._buf[o: o + nbytes]
+
+    def barrier(self, channel: int):
+        pass
+
+    def resync(self):
+        pass
+
+
 class _SymmetricBuffers:
     """One symmetric-memory allocation per rank cut into named regions, the peers' addresses of every region, and
     the extension's bounded barrier on per-peer signal words (two independent sets, "channels")."""

@@ -267,6 +267,16 @@ DLB_API int dlb_p2p_barrier(const void* const* peer_signals, int world, int my_r
  * row_pos[i] of rank row_rank[i] (negative: not sent). */
 DLB_API int dlb_p2p_all_gather_small(const void* src, int64_t bytes, int world, int my_rank, const void* const* peer_dst,
                              void* stream);
+/* The index arithmetic between the two: from the all-gathered counts [world, cnt_stride] (int32), this rank's expert ids
+ * topk_ids int64 [pairs] and their rank_in_expert (dlb_sort_by_expert) it writes, for the rank as a source, pair_rank /
+ * pair_row / pair_pos int32 [pairs] (pair_pos: row of the own return buffer, ordered by expert, then by that rank) and
+ * ids_sent (the id, -1 for a slot that is not sent: no expert, or the expert's block of rows_per_expert rows is full);
+ * for the rank as an owner, masked_m int32 [num_local_experts] and row_rank / row_pos int32
+ * [num_local_experts * rows_per_expert] as dlb_p2p_push_rows_indexed takes them. */
+DLB_API int dlb_p2p_ll_plan(const int32_t* counts, int cnt_stride, int world, int num_experts, int my_rank,
+                    int num_local_experts, int rows_per_expert, const int64_t* topk_ids, const int32_t* rank_in_expert,
+                    int64_t pairs, int32_t* pair_rank, int32_t* pair_row, int32_t* pair_pos, int32_t* ids_sent,
+                    int32_t* masked_m, int32_t* row_rank, int32_t* row_pos, void* stream);
 DLB_API int dlb_p2p_ll_quant_push(const void* x, int x_dtype, int64_t tokens, int64_t k, int64_t ldx, int mode, float eps,
                           const int32_t* pair_rank, const int32_t* pair_row, int top_k, int world,
                           const void* const* peer_q, const void* const* peer_scales, void* stream);

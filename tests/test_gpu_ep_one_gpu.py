@@ -152,3 +152,38 @@ def test_decode_exchange_with_emulated_ranks(world, max_tokens):
         ops.ep_gather(comb[r], ids32, ws[r].contiguous(), pair_pos.contiguous(), out)
         err = O.rel_frobenius(out.cpu(), refs[r])
         assert err < 2e-2, (r, err)
+
+
+@pytest.mark.parametrize("world,me,e,rpe,t,k", [(4, 2, 16, 12, 40, 4), (1, 0, 8, 16, 33, 2), (8, 7, 64, 24, 128, 8),
+                                                (2, 0, 6, 64, 5, 3)])
+def test_plan_kernel_equals_the_tensor_arithmetic(world, me, e, rpe, t, k):
+    """`dlb_p2p_ll_plan` against `make_low_latency_p2p_plan` (the same index arithmetic in plain tensor operations,
+    which the CPU tests cover): every output equal, with experts whose blocks overflow (rows dropped), experts
+    nobody chose and slots without an expert."""
+    from dlblas_b200 import _C, ops
+    from dlblas_b200.layers.moe.token_dispatcher import make_low_latency_p2p_plan
+    g = torch.Generator().manual_seed(world * 100 + me)
+    nle = e // world
+    ids = torch.randint(0, e, (t, k), generator=g)
+    ids[::7, 0] = -1
+    ids[:, -1] = torch.where(torch.rand(t, generator=g) < 0.5, torch.zeros(t, dtype=torch.int64), ids[:, -1])  # crowd expert 0
+    ids = ids.to(DEV)
+    _, _, _, rank_in, counts = ops.sort_by_expert(ids, e, want_rank=True, want_counts=True)
+    stride = (e + 3) // 4 * 4
+    allcnt = torch.randint(0, max(2, 2 * rpe // max(world, 1)), (world, stride), generator=g, dtype=torch.int32).to(DEV)
+    allcnt[:, 1] = 0                                              # an expert nobody chose
+    allcnt[me, :e] = counts
+    want = make_low_latency_p2p_plan(allcnt[:, :e].to(torch.int64), me, nle, rpe, ids, rank_in)
+    pairs = t * k
+    outs = [torch.full((n,), -7, dtype=torch.int32, device=DEV) for n in (pairs, pairs, pairs, pairs, nle, nle * rpe,
+                                                                          nle * rpe)]
+    pair_rank, pair_row, pair_pos, ids_sent, masked_m, row_rank, row_pos = outs
+    _C.check(_C.lib().dlb_p2p_ll_plan(_C.ptr(allcnt), stride, world, e, me, nle, rpe, _C.ptr(ids.view(-1)),
+                                      _C.ptr(rank_in), pairs, _C.ptr(pair_rank), _C.ptr(pair_row), _C.ptr(pair_pos),
+                                      _C.ptr(ids_sent), _C.ptr(masked_m), _C.ptr(row_rank), _C.ptr(row_pos),
+                                      torch.cuda.current_stream().cuda_stream))
+    w_rank, w_row, w_pos, w_sent, w_m, w_rrank, w_rpos = want
+    assert torch.equal(pair_rank, w_rank) and torch.equal(pair_row, w_row) and torch.equal(pair_pos, w_pos)
+    assert torch.equal(ids_sent, torch.where(w_sent, ids.view(-1), torch.full_like(ids.view(-1), -1)).to(torch.int32))
+    assert torch.equal(masked_m, w_m) and torch.equal(row_rank, w_rrank) and torch.equal(row_pos, w_rpos)
+    assert bool((~w_sent & (ids.view(-1) >= 0)).any()) or world == 2    # the crowded expert overflowed somewhere
