@@ -61,6 +61,7 @@ SIGNATURES = {
     "dlb_p2p_sum_push_cols": (c_int, [c_vp, c_int, c_vp, c_int, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp, c_i64, c_i64,
                                       c_int]),
     "dlb_p2p_push_rows": (c_int, [c_vp, c_i64, c_vp, c_int, c_int, c_i64, c_vp, c_vp]),
+    "dlb_p2p_push_rows_masked": (c_int, [c_vp, c_i64, c_vp, c_int, c_int, c_vp, c_vp, c_int, c_vp, c_vp]),
     "dlb_p2p_barrier": (c_int, [c_vp, c_int, c_int, c_vp, ctypes.c_uint64, c_vp, c_vp]),
     "dlb_p2p_ll_plan": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp,
                                 c_vp, c_vp, c_vp, c_vp]),

@@ -39,6 +39,43 @@ bool withhold_loads();  // dlb_set_wait_policy(): the GEMMs' load role issues no
 
 __host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Masked layouts ([experts, rows_per_expert, ...] with only the first masked_m[e] rows of expert e in use) hold a few
+// hundred valid rows among tens of thousands in a decode step.  These two helpers let a kernel walk the valid rows only:
+// every block builds the running sums of min(masked_m[e], cap) in shared memory (prefix[experts] = their total; warp 0
+// scans, all threads of the block must call), then item i of [0, total) is row i - prefix[e] of expert e.
+constexpr int MASKED_MAX_EXPERTS = 1024;
+#ifdef __CUDACC__
+__device__ inline void masked_prefix(const int* __restrict__ masked_m, int experts, int cap, int* prefix) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int carry = 0;
+    for (int e0 = 0; e0 < experts; e0 += 32) {
+      const int e = e0 + lane;
+      const int v = e < experts ? min(max(__ldg(masked_m + e), 0), cap) : 0;
+      int incl = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+      }
+      if (e < experts) prefix[e] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) prefix[experts] = carry;
+  }
+  __syncthreads();
+}
+// the expert that holds item `item` (< prefix[experts]): the last e with prefix[e] <= item
+__device__ inline int masked_find(const int* prefix, int experts, int item) {
+  int lo = 0, hi = experts;   // invariant: prefix[lo] <= item < prefix[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= item) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+#endif
+
 // ---- warp helpers -------------------------------------------------------- //
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

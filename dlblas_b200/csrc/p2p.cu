@@ -371,6 +371,28 @@ __global__ void __launch_bounds__(THREADS) push_rows_indexed_kernel(const uint4*
   }
 }
 
+// The same over a masked layout [experts, rows_per_expert]: only the first masked_m[e] rows of every expert are looked
+// at (one warp per valid row), not the whole layout.
+__global__ void __launch_bounds__(THREADS) push_rows_masked_kernel(const uint4* __restrict__ src, long long vec_per_row,
+                                                                   const int* __restrict__ masked_m, int experts,
+                                                                   int rows_per_expert, const int* __restrict__ row_rank,
+                                                                   const int* __restrict__ row_pos, PeerPtrs peer_dst) {
+  __shared__ int prefix[MASKED_MAX_EXPERTS + 1];
+  masked_prefix(masked_m, experts, rows_per_expert, prefix);
+  const int total = prefix[experts];
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * (THREADS / 32);
+  for (int item = blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5); item < total; item += warps) {
+    const int e = masked_find(prefix, experts, item);
+    const long long row = (long long)e * rows_per_expert + (item - prefix[e]);
+    const int r = __ldg(row_rank + row);
+    if (r < 0) continue;
+    const uint4* from = src + row * vec_per_row;
+    uint4* to = reinterpret_cast<uint4*>(peer_dst.p[r]) + (long long)__ldg(row_pos + row) * vec_per_row;
+    for (long long c = lane; c < vec_per_row; c += 32) to[c] = __ldg(from + c);
+  }
+}
+
 int grid_for(long long total_threads) {
   long long blocks = ceil_div(total_threads, THREADS);
   const long long cap = (long long)sm_count() * 16;
@@ -510,6 +532,28 @@ extern "C" int dlb_p2p_sum_push_cols(const void* y, int dtype, const int64_t* id
                                      int max_blocks) {
   return p2p_sum_push(y, dtype, ids, top_k, h, counts, world, my_rank, region_rows, peer_dst, stream, col_begin,
                       col_count, max_blocks);
+}
+
+extern "C" int dlb_p2p_push_rows_masked(const void* src, int64_t row_bytes, const int32_t* masked_m, int num_local_experts,
+                                        int rows_per_expert, const int32_t* row_rank, const int32_t* row_pos, int world,
+                                        const void* const* peer_dst, void* stream) {
+  DLB_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, DLB_ERR_INVALID,
+              "p2p_push_rows_masked: rows must be multiples of 16 bytes");
+  DLB_REQUIRE(num_local_experts > 0 && num_local_experts <= MASKED_MAX_EXPERTS && rows_per_expert > 0, DLB_ERR_INVALID,
+              "p2p_push_rows_masked: experts=%d (at most %d), rows_per_expert=%d", num_local_experts, MASKED_MAX_EXPERTS,
+              rows_per_expert);
+  DLB_REQUIRE(world > 0 && world <= MAX_WORLD, DLB_ERR_INVALID, "p2p_push_rows_masked: bad world");
+  DLB_REQUIRE(src && masked_m && row_rank && row_pos && (uintptr_t)src % 16 == 0, DLB_ERR_INVALID,
+              "p2p_push_rows_masked: null or misaligned pointer");
+  PeerPtrs pd;
+  int rc = fill_peers(pd, peer_dst, world, "p2p_push_rows_masked");
+  if (rc != DLB_OK) return rc;
+  push_rows_masked_kernel<<<2 * sm_count(), THREADS, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const uint4*>(src), row_bytes / 16, masked_m, num_local_experts, rows_per_expert, row_rank, row_pos,
+      pd);
+  count_launch();
+  DLB_CHECK_LAUNCH("push_rows_masked_kernel");
+  return DLB_OK;
 }
 
 extern "C" int dlb_p2p_barrier(const void* const* peer_signals, int world, int my_rank, uint32_t* counter,

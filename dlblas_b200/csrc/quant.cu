@@ -174,27 +174,32 @@ __global__ void __launch_bounds__(THREADS) silu_and_mul_kernel(const T* __restri
 }
 
 // silu(gate) * up, rounded like the reference, then the 1x128 quantisation of the result.  With masked_m (masked
-// layout: blockIdx.y = expert) only the expert's first masked_m[e] rows are visited at all; a decode step holds a few
-// hundred valid rows in a layout of tens of thousands.
+// layout, `experts` experts of rows_per_expert rows) only the valid rows are visited: a decode step holds a few
+// hundred of them in a layout of tens of thousands.
 template <typename T>
 __global__ void __launch_bounds__(THREADS) silu_mul_quant_kernel(const T* __restrict__ in, long long rows, long long n,
                                                                  int mode, float eps, int round_silu,
-                                                                 const int* __restrict__ masked_m,
+                                                                 const int* __restrict__ masked_m, int experts,
                                                                  long long rows_per_expert, uint8_t* __restrict__ q,
                                                                  float* __restrict__ scales) {
+  __shared__ int prefix[MASKED_MAX_EXPERTS + 1];
   const long long vec_per_row = n / 8;
   const long long groups = n / 128;
-  long long row_base = 0, my_rows = rows;
+  long long my_rows = rows;
   if (masked_m != nullptr) {
-    row_base = (long long)blockIdx.y * rows_per_expert;
-    my_rows = min((long long)__ldg(masked_m + blockIdx.y), rows_per_expert);
+    masked_prefix(masked_m, experts, (int)rows_per_expert, prefix);
+    my_rows = prefix[experts];
   }
   const long long total = my_rows * vec_per_row;
   for (long long u0 = (long long)blockIdx.x * THREADS; u0 < total; u0 += (long long)gridDim.x * THREADS) {
     const long long u = u0 + threadIdx.x;
     const bool active = u < total;
-    const long long row = row_base + (active ? u / vec_per_row : 0);
+    long long row = active ? u / vec_per_row : 0;
     const long long c = active ? (u % vec_per_row) * 8 : 0;
+    if (masked_m != nullptr && active) {
+      const int e = masked_find(prefix, experts, (int)row);
+      row = (long long)e * rows_per_expert + (row - prefix[e]);
+    }
     float h[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) h[i] = 0.f;
@@ -522,26 +527,24 @@ extern "C" int dlb_silu_mul_quant(const void* gate_up, int dtype, int64_t rows, 
   if (rows == 0) return DLB_OK;
   DLB_REQUIRE(gate_up && q && scales, DLB_ERR_INVALID, "silu_mul_quant: null pointer");
   DLB_REQUIRE((uintptr_t)gate_up % 16 == 0 && (uintptr_t)q % 8 == 0, DLB_ERR_INVALID, "silu_mul_quant: misaligned");
-  dim3 grid((unsigned)grid_for(rows * (n / 8)));
+  int grid = grid_for(rows * (n / 8));
+  int experts = 0;
   if (masked_m != nullptr) {
-    // One column of blocks per expert.  Most experts of a decode step hold no row or a handful, and a block that finds
-    // nothing to do still costs its launch: eight blocks per expert (16 k blocks at 64 per expert took 15 us to do
-    // 3 us of work).
-    DLB_REQUIRE(rows % rows_per_expert == 0 && rows / rows_per_expert <= 65535, DLB_ERR_INVALID,
-                "silu_mul_quant: rows=%lld must be a whole number (at most 65535) of experts of %lld rows", (long long)rows,
-                (long long)rows_per_expert);
-    grid = dim3((unsigned)min((long long)ceil_div(rows_per_expert * (n / 8), (int64_t)THREADS), 8ll),
-                (unsigned)(rows / rows_per_expert));
+    DLB_REQUIRE(rows % rows_per_expert == 0 && rows / rows_per_expert <= MASKED_MAX_EXPERTS, DLB_ERR_INVALID,
+                "silu_mul_quant: rows=%lld must be a whole number (at most %d) of experts of %lld rows", (long long)rows,
+                MASKED_MAX_EXPERTS, (long long)rows_per_expert);
+    experts = (int)(rows / rows_per_expert);
+    grid = min(grid, 4 * sm_count());   // the valid rows are few; every block pays for the running sums
   }
   cudaStream_t st = (cudaStream_t)stream;
   uint8_t* qq = reinterpret_cast<uint8_t*>(q);
   if (dtype == DLB_BF16)
     silu_mul_quant_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(gate_up), rows,
                                                                   n, quant_mode, eps, round_silu, masked_m,
-                                                                  rows_per_expert, qq, scales);
+                                                                  experts, rows_per_expert, qq, scales);
   else if (dtype == DLB_F16)
     silu_mul_quant_kernel<__half><<<grid, THREADS, 0, st>>>(reinterpret_cast<const __half*>(gate_up), rows, n, quant_mode,
-                                                           eps, round_silu, masked_m, rows_per_expert, qq, scales);
+                                                           eps, round_silu, masked_m, experts, rows_per_expert, qq, scales);
   else
     return fail(DLB_ERR_INVALID, "silu_mul_quant: unsupported dtype %d (bf16 / fp16)", dtype);
   count_launch();

@@ -541,7 +541,7 @@ class TokenDispatcherLowLatencyP2P:
             hidden_states.stride(0), _C.QUANT_DIV_EPS, 1e-10, _C.ptr(pair_rank), _C.ptr(pair_row), k, w,
             sym.peers["q"], sym.peers["s"], _C.stream(dev)))
         sym.barrier(0)
-        plan = (pair_pos.view(t, k), ids_sent.view(t, k), row_rank, row_pos, t, pair_row.view(t, k))
+        plan = (pair_pos.view(t, k), ids_sent.view(t, k), row_rank, row_pos, t, pair_row.view(t, k), masked_m)
         return [self.recv_q, self.recv_s], masked_m, plan, _record_event(), (lambda: None)
 
     def combine(self, hidden_states: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor):
@@ -553,7 +553,7 @@ class TokenDispatcherLowLatencyP2P:
                       handle: Tuple, async_finish: bool):
         assert topk_idx.dtype == torch.int64
         assert topk_weights.dtype == torch.float32
-        pair_pos, ids_sent, row_rank, row_pos, t, pair_row = handle
+        pair_pos, ids_sent, row_rank, row_pos, t, pair_row, masked_m = handle
         nle, rpe, h = hidden_states.shape
         assert hidden_states.dtype == self.comb.dtype and hidden_states.is_contiguous()
         dev = hidden_states.device
@@ -563,9 +563,9 @@ class TokenDispatcherLowLatencyP2P:
             # one rank: a token's rows are in this GPU's own layout; out[t] = sum_k w[t, k] * layout[pair_row[t, k]]
             ops.ep_gather(hidden_states.view(nle * rpe, h), ids_sent, topk_weights.contiguous(), pair_row, out)
             return out, _record_event(), (lambda: None)
-        _C.check(_C.lib().dlb_p2p_push_rows_indexed(_C.ptr(hidden_states), h * hidden_states.element_size(), nle * rpe,
-                                                   _C.ptr(row_rank), _C.ptr(row_pos), self.world_size,
-                                                   sym.peers["comb"], _C.stream(dev)))
+        _C.check(_C.lib().dlb_p2p_push_rows_masked(_C.ptr(hidden_states), h * hidden_states.element_size(),
+                                                  _C.ptr(masked_m), nle, rpe, _C.ptr(row_rank), _C.ptr(row_pos),
+                                                  self.world_size, sym.peers["comb"], _C.stream(dev)))
         sym.barrier(1)
         # out[t] = sum_k w[t, k] * comb[pair_pos[t, k]]
         ops.ep_gather(self.comb, ids_sent, topk_weights.contiguous(), pair_pos, out)

@@ -282,6 +282,12 @@ DLB_API int dlb_p2p_ll_quant_push(const void* x, int x_dtype, int64_t tokens, in
                           const void* const* peer_q, const void* const* peer_scales, void* stream);
 DLB_API int dlb_p2p_push_rows_indexed(const void* src, int64_t row_bytes, int64_t rows, const int32_t* row_rank,
                               const int32_t* row_pos, int world, const void* const* peer_dst, void* stream);
+/* The same for a masked layout [num_local_experts, rows_per_expert, row_bytes] of which only the first masked_m[e] rows
+ * of every expert are in use: the kernel walks those rows only (a decode step uses a few hundred of tens of
+ * thousands). */
+DLB_API int dlb_p2p_push_rows_masked(const void* src, int64_t row_bytes, const int32_t* masked_m, int num_local_experts,
+                             int rows_per_expert, const int32_t* row_rank, const int32_t* row_pos, int world,
+                             const void* const* peer_dst, void* stream);
 
 /* ---- 16-bit grouped GEMM -----------------------------------------------------------------
  * m_grouped_gemm with trans_b = True (dlblas/kernels/grouped_gemm/BF16/m_grouped_gemm.py:235-352):

@@ -138,8 +138,12 @@ def test_decode_exchange_with_emulated_ranks(world, max_tokens):
     for r in range(world):                                     # phase 2: masked-layout experts, rows back to their source
         masked_m, row_rank, row_pos = plans[r][4], plans[r][5], plans[r][6]
         out_states = layer.experts([q[r].view(FP8), s[r]], *local[r], masked_m, 0)
-        _C.check(lib.dlb_p2p_push_rows_indexed(_C.ptr(out_states), h * 2, nle * rpe, _C.ptr(row_rank), _C.ptr(row_pos),
-                                               world, pcomb, st))
+        if world == 2:
+            _C.check(lib.dlb_p2p_push_rows_indexed(_C.ptr(out_states), h * 2, nle * rpe, _C.ptr(row_rank),
+                                                   _C.ptr(row_pos), world, pcomb, st))
+        else:                                                  # the same walk over the valid rows only
+            _C.check(lib.dlb_p2p_push_rows_masked(_C.ptr(out_states), h * 2, _C.ptr(masked_m), nle, rpe,
+                                                  _C.ptr(row_rank), _C.ptr(row_pos), world, pcomb, st))
     _C.check_status()
     for r in range(world):                                     # phase 3: weighted gather on the source
         t = tokens[r]
