@@ -124,14 +124,19 @@ def test_fused_moe_v3_contiguous_entry_point():
                         None).dtype == torch.bfloat16
 
 
-def test_low_latency_masked_experts_single_rank():
-    """FusedMoELowLatency on one rank: dispatch to the masked layout, masked GEMMs, weighted combine."""
+@pytest.mark.parametrize("backend", ["p2p", "nccl"])
+def test_low_latency_masked_experts_single_rank(backend, monkeypatch):
+    """FusedMoELowLatency on one rank: dispatch to the masked layout, masked GEMMs, weighted combine; with the
+    peer-to-peer dispatcher on this GPU's own memory (the default) and with the all-to-all dispatcher's one-rank plan."""
     from dlblas_b200 import _C
     from dlblas_b200.layers.moe.ep_moe import build_deepep_moe
+    monkeypatch.setenv("DLBLAS_EP_BACKEND", backend)
     t, h, inter, e, k = 100, 512, 256, 16, 4
     x, logits, w13, w13s, w2, w2s = O.make_layer_inputs(t, h, inter, e, seed=6)
     ow, oids = O.softmax_topk(logits, k, True)
     layer = build_deepep_moe(True, 1, None, e, h, 128, k, torch.bfloat16)
+    assert type(layer.token_dispatcher).__name__ == ("TokenDispatcherLowLatencyP2P" if backend == "p2p"
+                                                     else "TokenDispatcherLowLatency")
     out = layer.forward(x.to(DEV), ow.to(DEV), oids.to(DEV), *_to_dev(w13, w13s, w2, w2s))
     _C.check_status()
     ref = O.moe_layer(x, ow, oids, w13, w13s, w2, w2s, top_k=k)
