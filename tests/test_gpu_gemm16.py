@@ -108,3 +108,20 @@ def test_k_grouped_gemm_like_the_reference_test():
         ref = utils.gmm_dw(a, b, sizes.cpu())
         torch.testing.assert_close(utils.row_max_normalization(out.float()), utils.row_max_normalization(ref.float()),
                                    rtol=0.01, atol=0.01)
+
+
+def test_k_grouped_gemm_sizes_that_do_not_add_up():
+    """Group sizes that stop short of the operands' rows leave the rest unused; sizes that run past them are clipped
+    (the last groups shrink, down to empty), as the entry point documents."""
+    from dlblas_b200 import _C
+    from dlblas_b200.kernels.grouped_gemm.BF16 import k_grouped_gemm
+    g = torch.Generator().manual_seed(23)
+    k, m, n = 300, 256, 136
+    a = (torch.randn(k, m, generator=g) * 0.5).to(torch.bfloat16)
+    b = (torch.randn(k, n, generator=g) * 0.5).to(torch.bfloat16)
+    for sizes, clipped in (([100, 50], [100, 50]), ([200, 150, 70], [200, 100, 0])):
+        out = k_grouped_gemm(a.to(DEV), b.to(DEV), torch.tensor(sizes, dtype=torch.int64, device=DEV))
+        _C.check_status()
+        ref = O.k_grouped_gemm(a, b, torch.tensor(clipped, dtype=torch.int64))
+        assert O.rel_frobenius(out.cpu(), ref) < 2e-3
+        assert not out[-1].any() or clipped[-1] > 0
