@@ -587,7 +587,7 @@ __global__ void k_group_plan_kernel(const long long* __restrict__ sizes, int gro
   }
 }
 
-// Tile lists for the workers of the GEMM (one block, at least `workers` threads).  Tiles are handed out in tile order,
+// Tile lists for the workers of the GEMM, built in two steps.  Tiles are handed out in tile order,
 // group by group, each to the worker that a greedy scheduler would find free first, with a tile's cost taken as its
 // K blocks (at least KG_MIN_COST, the part of a tile that does not shrink with K).  All tiles of a group cost the same,
 // so inside a group the order of the workers by the time they become free does not change: tile l of the group goes to
@@ -597,20 +597,23 @@ __global__ void k_group_plan_kernel(const long long* __restrict__ sizes, int gro
 // the operands were then read from DRAM 4.4 times instead of 2 (32 groups, K ranges uniform in 0 ... 10 k).
 constexpr int KG_MIN_COST = 8;
 
+// Step 1, one small block (the loop over the groups is sequential and pays one block barrier per group, so the block is
+// no larger than the workers need): for every group the workers in the order in which they become free (who_of) and
+// how many tiles each already holds (held_before); at the end every worker's tile count.
 __global__ void __launch_bounds__(256)
 k_group_schedule_kernel(const int4* __restrict__ kseg, int groups, int tiles_per_group, int workers,
-                        int* __restrict__ sched, int* __restrict__ sched_count, int sched_stride) {
-  // The workers in the order in which they become free, double-buffered: free_at[b][r] and who[b][r] for rank r.
+                        int* __restrict__ who_of, int* __restrict__ held_before, int* __restrict__ sched_count) {
+  // free_at[b][r] and who[b][r] for rank r, double-buffered so that a group needs one barrier
   __shared__ long long free_at[2][256];
   __shared__ int who[2][256];
-  __shared__ int count[256];   // tiles given to each worker so far
-  __shared__ int cost_of[1024]; // the groups' tile costs, 1024 groups at a time (one global load per group would sit
-                                // on the critical path of the loop below)
+  __shared__ int held_of[2][256]; // a worker changes rank from group to group: its tile count travels with it
+  __shared__ int cost_of[1024];   // the groups' tile costs, 1024 groups at a time (one global load per group would
+                                  // sit on the critical path of the loop below)
   const int r = threadIdx.x;
   if (r < workers) {
     free_at[0][r] = 0;
     who[0][r] = r;
-    count[r] = 0;
+    held_of[0][r] = 0;
   }
   __syncthreads();
   const int full = tiles_per_group / workers, rest = tiles_per_group - full * workers;
@@ -621,20 +624,16 @@ k_group_schedule_kernel(const int4* __restrict__ kseg, int groups, int tiles_per
         cost_of[j] = max(KG_MIN_COST, __ldg(&kseg[g + j]).y);
       __syncthreads();
     }
-    for (int l = threadIdx.x; l < tiles_per_group; l += blockDim.x) {
-      const int round = l / workers, to = who[cur][l - round * workers];
-      sched[(long long)to * sched_stride + count[to] + round] = g * tiles_per_group + l;
-    }
     // The first `rest` workers take one tile more than the others.  Both parts stay sorted, so the new order is a merge
     // of the two: each worker finds its new rank with one binary search in the other part.
     const long long cost = cost_of[g & 1023];
-    int new_rank = 0, me = 0, got = 0;
-    long long mine = 0;
     if (r < workers) {
-      me = who[cur][r];
-      got = full + (r < rest ? 1 : 0);
-      mine = free_at[cur][r] + got * cost;
-      int lo, hi;
+      const int me = who[cur][r], held = held_of[cur][r];
+      who_of[(long long)g * workers + r] = me;
+      held_before[(long long)g * workers + r] = held;      // indexed by rank, like who_of
+      const int got = full + (r < rest ? 1 : 0);
+      const long long mine = free_at[cur][r] + got * cost;
+      int lo, hi, new_rank;
       if (r < rest) {   // after the workers of the other part that are free no later
         lo = rest, hi = workers;
         while (lo < hi) {
@@ -650,16 +649,27 @@ k_group_schedule_kernel(const int4* __restrict__ kseg, int groups, int tiles_per
         }
         new_rank = (r - rest) + lo;
       }
-    }
-    __syncthreads();   // everybody has read count[] and this buffer
-    if (r < workers) {
-      count[me] += got;
       free_at[cur ^ 1][new_rank] = mine;
       who[cur ^ 1][new_rank] = me;
+      held_of[cur ^ 1][new_rank] = held + got;
     }
     __syncthreads();
   }
-  if (r < workers) sched_count[r] = count[r];
+  if (r < workers) sched_count[who[cur][r]] = held_of[cur][r];
+}
+
+// Step 2, one thread per tile: tile l of group g goes to the worker at rank l mod workers of that group's order, behind
+// the tiles the worker already holds.
+__global__ void __launch_bounds__(256)
+k_group_tile_lists_kernel(const int* __restrict__ who_of, const int* __restrict__ held_before, int groups,
+                          int tiles_per_group, int workers, int* __restrict__ sched, int sched_stride) {
+  const long long total = (long long)groups * tiles_per_group;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int g = (int)(t / tiles_per_group), l = (int)(t - (long long)g * tiles_per_group);
+    const int round = l / workers, rank = l - round * workers;
+    const long long at = (long long)g * workers + rank;
+    sched[(long long)__ldg(who_of + at) * sched_stride + __ldg(held_before + at) + round] = (int)t;
+  }
 }
 
 // Maps, arguments and launch shared by the two entry points.  The tensor maps see a as [a_map_rows, a_row_bytes] and b
@@ -768,7 +778,8 @@ extern "C" int64_t dlb_k_grouped_gemm_workspace_bytes(int64_t k_total, int64_t m
   const int64_t m_tiles = ceil_div(m, (int64_t)tile_rows);
   const int64_t per_group = m_tiles * ceil_div(n, (int64_t)BN);
   // tile lists: at most per_group / workers + 1 tiles per group and worker; sized for any worker count up to 256
-  const int64_t sched_ints = 256 + num_groups * (per_group + 256);
+  // + per group the workers' order and their tile counts before the group (two ints per worker, up to 256 workers)
+  const int64_t sched_ints = 256 + num_groups * (per_group + 256) + 2 * (int64_t)num_groups * 256;
   return 16 * (1 + num_groups * m_tiles) + 16 * (int64_t)num_groups + 4 * sched_ints;
 }
 
@@ -813,8 +824,16 @@ extern "C" int dlb_k_grouped_gemm_16bit(const void* a, const void* b, int dtype,
                                          tile_rows, kseg, tiles);
   if ((rc = check_cuda(cudaGetLastError(), "k_group_plan_kernel")) != DLB_OK) return rc;
   count_launch();
-  k_group_schedule_kernel<<<1, 256, 0, st>>>(kseg, num_groups, (int)per_group, workers, sched, sched_count, sched_stride);
+  int* who_of = sched + (long long)num_groups * (per_group + 256);
+  int* held_before = who_of + (long long)num_groups * 256;
+  const int sched_threads = (workers + 31) / 32 * 32;
+  k_group_schedule_kernel<<<1, sched_threads, 0, st>>>(kseg, num_groups, (int)per_group, workers, who_of, held_before,
+                                                       sched_count);
   if ((rc = check_cuda(cudaGetLastError(), "k_group_schedule_kernel")) != DLB_OK) return rc;
+  count_launch();
+  k_group_tile_lists_kernel<<<(unsigned)min((long long)ceil_div(all_tiles, (int64_t)256), 1024ll), 256, 0, st>>>(
+      who_of, held_before, num_groups, (int)per_group, workers, sched, sched_stride);
+  if ((rc = check_cuda(cudaGetLastError(), "k_group_tile_lists_kernel")) != DLB_OK) return rc;
   count_launch();
   return run_gemm16(a, k_total, 2 * m, 64, b, k_total, 2 * n, 64, dtype, m, n, 64, kseg, false, 0, m,
                     reinterpret_cast<const int32_t*>(tiles), (int)(num_groups * m_tiles), tile_rows, c, n, status, stream,
