@@ -167,3 +167,45 @@ def test_topk_gating_gradient_against_reference_backward(golden):
             return float(l.double() * 0.7 + (w.double() * c["grad_weights"].double()).sum())
         fd = (f(x + d) - f(x - d)) / 2e-4
         assert abs(fd - float(true[3, 1])) < 5e-2 * max(1.0, abs(fd))
+
+
+def test_k_grouped_gemm_oracle_against_the_reference_ground_truth():
+    """`O.k_grouped_gemm` against the ground truth of the reference's own test (gmm_dw,
+    tests/kernels/grouped_gemm/BF16/test_k_grouped_gemm.py:10-28: `lhs.T @ rhs` per group of the shared leading
+    dimension), computed here in float64 and under that test's row-max normalisation and tolerance."""
+    g = torch.Generator().manual_seed(31)
+    sizes = torch.tensor([37, 0, 64, 5, 130], dtype=torch.int64)
+    k, m, n = int(sizes.sum()), 24, 40
+    a = torch.randn(k, m, generator=g).to(torch.bfloat16)
+    b = torch.randn(k, n, generator=g).to(torch.bfloat16)
+    out = O.k_grouped_gemm(a, b, sizes)
+    assert out.shape == (5, m, n) and out.dtype == torch.bfloat16 and not out[1].any()
+    start = 0
+    for i, s in enumerate(sizes.tolist()):
+        want = a[start:start + s].double().t() @ b[start:start + s].double()
+        start += s
+        norm = want.abs().max(dim=-1).values + 1e-9
+        torch.testing.assert_close(out[i].double() / norm[:, None], want / norm[:, None], rtol=0.01, atol=0.01)
+
+
+def test_unquantised_fused_moe_oracle_against_a_dense_formulation():
+    """`O.fused_moe_16bit` (per token and slot, with the reference's rounding points) against the same layer written
+    as dense per-expert matrix products in float64: they differ only by the 16-bit roundings of the intermediates."""
+    g = torch.Generator().manual_seed(32)
+    t, h, inter, e, k = 20, 32, 48, 4, 2
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(e, 2 * inter, h, generator=g) * 0.2).to(torch.bfloat16)
+    w2 = (torch.randn(e, h, inter, generator=g) * 0.2).to(torch.bfloat16)
+    weights, ids = O.softmax_topk(torch.randn(t, e, generator=g), k, True)
+    ids[3, 1] = -1
+    out = O.fused_moe_16bit(x, w1, w2, weights, ids)
+    want = torch.zeros(t, h, dtype=torch.float64)
+    for ex in range(e):
+        c1 = x.double() @ w1[ex].double().t()
+        act = c1[:, :inter] / (1.0 + torch.exp(-c1[:, :inter])) * c1[:, inter:]
+        y = act @ w2[ex].double().t()
+        for j in range(k):
+            sel = ids[:, j] == ex
+            want[sel] += weights[sel, j].double()[:, None] * y[sel]
+    assert out.dtype == torch.bfloat16
+    assert float((out.double() - want).norm() / want.norm()) < 1e-2
