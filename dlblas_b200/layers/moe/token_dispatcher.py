@@ -519,9 +519,12 @@ class TokenDispatcherLowLatencyP2P:
         _, _, _, rank_in, counts = ops.sort_by_expert(topk_idx, e, want_rank=True, want_counts=True)
         if self.cnt_ints != e:
             counts = torch.cat([counts, counts.new_zeros(self.cnt_ints - e)])
-        _C.check(_C.lib().dlb_p2p_all_gather_small(_C.ptr(counts), self.cnt_ints * 4, w, me, sym.peers["allcnt"],
-                                                  _C.stream(dev)))
-        sym.barrier(0)
+        cnt_matrix = counts                                          # one rank: its own counts are the whole matrix
+        if w > 1:
+            _C.check(_C.lib().dlb_p2p_all_gather_small(_C.ptr(counts), self.cnt_ints * 4, w, me, sym.peers["allcnt"],
+                                                      _C.stream(dev)))
+            sym.barrier(0)
+            cnt_matrix = self.allcnt
         # where every pair goes and where every row of the own layout came from: one kernel on the gathered counts
         # (the peers overwrite them only after this rank has passed the combine's barrier); the same arithmetic in
         # plain tensor operations is `make_low_latency_p2p_plan`
@@ -532,7 +535,7 @@ class TokenDispatcherLowLatencyP2P:
         row_rank = plan_ints[4 * pairs + nle:4 * pairs + nle + nle * rpe]
         row_pos = plan_ints[4 * pairs + nle + nle * rpe:]
         ids_flat = topk_idx.contiguous().view(-1)
-        _C.check(_C.lib().dlb_p2p_ll_plan(_C.ptr(self.allcnt), self.cnt_ints, w, e, me, nle, rpe, _C.ptr(ids_flat),
+        _C.check(_C.lib().dlb_p2p_ll_plan(_C.ptr(cnt_matrix), self.cnt_ints, w, e, me, nle, rpe, _C.ptr(ids_flat),
                                           _C.ptr(rank_in), pairs, _C.ptr(pair_rank), _C.ptr(pair_row), _C.ptr(pair_pos),
                                           _C.ptr(ids_sent), _C.ptr(masked_m), _C.ptr(row_rank), _C.ptr(row_pos),
                                           _C.stream(dev)))
